@@ -360,6 +360,50 @@ int b200_memcpy_h2d(void* dst, const void* src_host, long bytes, void* stream);
  * launching stream. */
 float b200_engine_last_decode_ms(const b200_engine* e);
 
+/* ------------------------------------------------------------------------- */
+/* Layer-level ops (csrc/layer_ops.cu; also built alone as libb200lm.so) for   */
+/* decoder designs assembled layer by layer on the host (models/layer_ops.py). */
+/* fp32 activations, bf16 weights; `cache_bf16` / `round_x` select the bf16    */
+/* serving mode (cache rows and matrix operands rounded to bf16) or true fp32. */
+/* ------------------------------------------------------------------------- */
+/* x[t] = embed[tokens[t]] * scale */
+int b200_lm_embed(const int* tokens, const void* embed, float scale, float* x, int T, int W, int vocab, void* stream);
+/* cs[t][i] = (cos, sin)(pos[t] * inv_freq[i]), angle in double precision; inv_freq[half] doubles on the device */
+int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T, int half, void* stream);
+/* n = y / sqrt(mean(y^2) + eps) * (w_offset + w); x = n or (add) x += n.  wgt != NULL: y row t is the weighted
+ * sum of rows t*top .. t*top+top-1 of y.  rows != NULL: the input row of output t is rows[t]. */
+int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const void* w, float w_offset, float eps,
+                      float* x, long ldx, int add, const int* rows, int T, int N, void* stream);
+/* D[t] = [q latent | kv latent | rotated key part] (the fused down-projection): cq = rmsnorm(q latent) * wq;
+ * own_kv: rmsnorm(kv latent) * wkv and the rotated part go to cache[slot[t]][pos[t]] = [kv_rank | rot_dim] */
+int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wkv, float eps, float* cq, long ldq,
+                        void* cache, int cache_bf16, long slot_stride, long tok_stride, const int* slot,
+                        const int* pos, const float* cs, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                        int own_kv, int T, void* stream);
+/* qa[t][h][kv_rank + i] = rotate-half rotary of q[t][h][dim + i] (first rot_dims of rot_dim) */
+int b200_lm_rope_q(const float* q, long ldq, int qh_stride, int dim, float* qa, long ldqa, int Dl, int kv_rank,
+                   const float* cs, int H, int rot_dim, int rot_dims, int T, void* stream);
+/* absorbed latent attention: out[t][h] = softmax_j(scale * qa[t][h] . cache[slot[t]][j]) . cache[..][j][0:kv_rank],
+ * j = 0..pos[t] */
+int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int cache_bf16, long slot_stride,
+                             long tok_stride, const int* slot, const int* pos, float* out, long ldo, int H, int Dl,
+                             int kv_rank, float scale, int round_q, int T, void* stream);
+/* the `top` largest of z[t][0..E) (lowest index wins a tie) and the softmax over them */
+int b200_lm_router_topk(const float* z, long ldz, int E, int top, int* idx, float* wgt, int T, void* stream);
+/* list[e][0..count[e]) = the entries i (ascending) with idx[i] == e */
+int b200_lm_moe_group(const int* idx, int n_entries, int E, int* list, long list_stride, int* count, void* stream);
+/* Y[b][r][n] = epi(sum_k X[b][xr][k] W[b][n][k] + bias[n]); list/count: rows of batch b are the entries
+ * list[b][0..count[b]), x row = entry / x_div, y row = entry.  epi 0 none, 1 relu^2, 2 p*tanh(v/p).
+ * skinny != 0: the decode kernel (a warp per weight row). */
+int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw, long wb, const void* bias, float* Y,
+                      long ldy, long yb, const int* list, long list_stride, const int* count, int x_div, int M, int N,
+                      int K, int batch, int epi, float epi_param, int round_x, int skinny, void* stream);
+/* greedy: lowest index of the largest logit per row and its log-probability */
+int b200_lm_argmax_rows(const float* z, long ldz, int V, int* tok, float* logprob, int B, void* stream);
+/* device-side token feedback of a decode loop: tok = sampled, pos += 1 for active rows; log[step][b] = sampled */
+int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* active, int* log, int log_stride, int step,
+                         int B, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -105,7 +105,29 @@ SIGNATURES = {
     "b200_engine_last_decode_ms": (_F, [_P]),
 }
 
+# the layer-level ops (csrc/layer_ops.cu): in libb200vlm.so and, alone, in libb200lm.so
+_D = C.c_double
+LM_SIGNATURES = {
+    "b200_last_error": (C.c_char_p, []),
+    "b200_abi_version": (_I, []),
+    "b200_device_check": (_I, [_I, C.POINTER(_I)]),
+    "b200_lm_embed": (_I, [_P, _P, _F, _P, _I, _I, _I, _P]),
+    "b200_lm_rope_table": (_I, [_P, _P, _P, _I, _I, _P]),
+    "b200_lm_norm_rows": (_I, [_P, _L, _P, _I, _P, _F, _F, _P, _L, _I, _P, _I, _I, _P]),
+    "b200_lm_latent_post": (_I, [_P, _L, _P, _P, _F, _P, _L, _P, _I, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "b200_lm_rope_q": (_I, [_P, _L, _I, _I, _P, _L, _I, _I, _P, _I, _I, _I, _I, _P]),
+    "b200_lm_latent_attention": (_I, [_P, _L, _P, _I, _L, _L, _P, _P, _P, _L, _I, _I, _I, _F, _I, _I, _P]),
+    "b200_lm_router_topk": (_I, [_P, _L, _I, _I, _P, _P, _I, _P]),
+    "b200_lm_moe_group": (_I, [_P, _I, _I, _P, _L, _P, _P]),
+    "b200_lm_gemm_rows": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _I,
+                               _I, _P]),
+    "b200_lm_argmax_rows": (_I, [_P, _L, _I, _P, _P, _I, _P]),
+    "b200_lm_advance_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
+}
+SIGNATURES.update(LM_SIGNATURES)
+
 _lib = None
+_lm_lib = None
 
 
 def lib() -> C.CDLL:
@@ -127,9 +149,24 @@ def lib() -> C.CDLL:
     return _lib
 
 
-def check(rc: int, what: str = "") -> None:
+def lm_lib() -> C.CDLL:
+    """The layer-level ops: libb200lm.so, compiled on first use (two small files; the build is skipped when
+    its sources are unchanged).  Raises if it cannot be built or loaded; there is no fallback."""
+    global _lm_lib
+    if _lm_lib is None:
+        from .build import build
+        l = C.CDLL(build(target="b200lm"))
+        for name, (res, args) in LM_SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lm_lib = l
+    return _lm_lib
+
+
+def check(rc: int, what: str = "", which=None) -> None:
     if rc != OK:
-        msg = lib().b200_last_error().decode(errors="replace")
+        msg = (which or _lib or _lm_lib or lib()).b200_last_error().decode(errors="replace")
         raise B200Error(f"{what or 'b200 call'} failed (code {rc}): {msg}")
 
 

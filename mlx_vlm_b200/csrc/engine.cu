@@ -13,18 +13,6 @@
 
 namespace b200 {
 
-static thread_local char g_err[1024] = "";
-void set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_err, sizeof(g_err), fmt, ap);
-  va_end(ap);
-}
-int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
-  set_error("CUDA error %d (%s) at %s:%d in %s", (int)e, cudaGetErrorString(e), file, line, what);
-  return B200_ERR_CUDA;
-}
-
 struct VBlk {
   const bf16 *ln1w, *ln1b, *ln2w, *ln2b, *qkvw, *qkvb, *projw, *projb, *fc1w, *fc1b, *fc2w, *fc2b;
 };
@@ -754,21 +742,6 @@ static int prefill_layers_v2_body(b200_engine* e, const int* pos3, int T, int ct
 }
 
 extern "C" {
-
-const char* b200_last_error(void) { return g_err; }
-int b200_abi_version(void) { return B200_ABI_VERSION; }
-
-int b200_device_check(int device, int* sm_count) {
-  cudaDeviceProp prop;
-  B200_CUDA(cudaGetDeviceProperties(&prop, device));
-  if (prop.major != 10) {
-    set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
-              prop.minor);
-    return B200_ERR_UNSUPPORTED;
-  }
-  if (sm_count) *sm_count = prop.multiProcessorCount;
-  return B200_OK;
-}
 
 int b200_engine_create(const b200_qwen2vl_config* cfg, int device, b200_engine** out) {
   B200_REQUIRE(cfg && out, "engine_create: null argument");

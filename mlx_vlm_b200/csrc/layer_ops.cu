@@ -1,0 +1,624 @@
+// Layer-level ops for decoder designs that are assembled layer by layer on the host (models/layer_ops.py):
+//   * fp32 residual stream with the norm on the sublayer's OUTPUT (x += norm(y)), RMS norms whose weight is
+//     stored either plainly or around zero (`w_offset`),
+//   * latent attention: queries through a low-rank latent, keys / values expanded from ONE cached latent row
+//     per token (+ one rotated key part shared by all heads).  The cache holds [latent | rotated part] rows;
+//     attention runs in the ABSORBED form: the key up-projection is folded into the query
+//     (q~_h = W_uk,h^T q_h, one row of kv_rank numbers per head), scores are q~_h . c_j + q_rot,h . k_rot,j, the
+//     softmax-weighted sum is taken over the latent rows themselves and the value up-projection is applied to
+//     that sum afterwards.  Every query token names its cache row (slot) and position, so a whole prompt, a
+//     portion of one, one decoded token and a batch of unequal requests are the same launch,
+//   * rotate-half rotary on the first `dims` numbers of a vector, angles from a double-precision table,
+//   * mixture of experts: fp32 router logits -> top-k (lowest index wins ties) -> softmax over the chosen
+//     logits; tokens are grouped per expert and the expert GEMMs run as ONE grouped launch each,
+//   * a general row GEMM  Y = X . W^T  with bf16 weights and fp32 accumulation in a fixed k order (the result
+//     of a row never depends on which other rows are in the launch), optionally batched (heads, experts) and
+//     gathered / scattered through row lists, and its skinny sibling for decode steps (a warp per weight row).
+// fp32 buffers everywhere except the weights (bf16) and, in the bf16 serving mode, the cache rows and the
+// operands of the matrix products (rounded to bf16 on load: `round_x`).
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+__device__ __forceinline__ float ld_act(const float* p) { return *p; }
+__device__ __forceinline__ float ld_act(const bf16* p) { return bf2f(*p); }
+__device__ __forceinline__ void st_act(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st_act(bf16* p, float v) { *p = f2bf(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];   // same order in every thread
+  return t;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// embedding: x[t] = embed[token[t]] * scale  (fp32)
+__global__ void embed_scale_kernel(const int* __restrict__ tok, const bf16* __restrict__ emb, float scale,
+                                   float* __restrict__ x, int W, int vocab) {
+  const int t = blockIdx.x;
+  int id = tok[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) x[(long)t * W + i] = bf2f(emb[(long)id * W + i]) * scale;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// rotary table: cs[t][i] = (cos, sin)(pos[t] * inv_freq[i]) with the angle in double precision
+__global__ void rope_table_kernel(const int* __restrict__ pos, const double* __restrict__ inv_freq,
+                                  float2* __restrict__ cs, int T, int half) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * half) return;
+  const double a = (double)pos[i / half] * inv_freq[i % half];
+  double s, c;
+  sincos(a, &s, &c);
+  cs[i] = make_float2((float)c, (float)s);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// RMS norm of y's rows (optionally the weighted sum of `top` rows of a scattered buffer), weight (w_offset + w),
+// then either out = norm or x += norm.  rows: optional gather list for the input row.
+struct NormP {
+  const float* y; long ldy;
+  const float* wgt; int top;          // combine: y row = sum_s wgt[t*top+s] * y[(t*top+s)]
+  const bf16* w; float w_offset, eps;
+  float* x; long ldx;                 // x += norm  (add != 0)  or  x = norm
+  int add;
+  const int* rows;                    // input row of output t (NULL: t)
+  int N;
+};
+__global__ void norm_rows_kernel(NormP p) {
+  extern __shared__ float sm[];
+  float* row = sm;                    // N
+  float* red = sm + p.N;              // 32
+  const int t = blockIdx.x;
+  const long r = p.rows ? p.rows[t] : t;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < p.N; i += blockDim.x) {
+    float v;
+    if (p.top > 0) {
+      v = 0.f;
+      for (int s = 0; s < p.top; ++s) v += p.wgt[r * p.top + s] * p.y[(r * p.top + s) * p.ldy + i];
+    } else {
+      v = p.y[r * p.ldy + i];
+    }
+    row[i] = v;
+    ss += v * v;
+  }
+  const float tot = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(tot / (float)p.N + p.eps);
+  for (int i = threadIdx.x; i < p.N; i += blockDim.x) {
+    const float v = row[i] * inv * (p.w_offset + bf2f(p.w[i]));
+    float* o = p.x + (long)t * p.ldx + i;
+    *o = p.add ? *o + v : v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// after the fused down-projection D[t] = [ q latent (q_rank) | kv latent (kv_rank) | key rot part (rot_dim) ]:
+// cq = rms(q latent) * wq ; c = rms(kv latent) * wkv -> cache[slot][pos][0:kv_rank] ; rope(rot part) -> cache[..][kv_rank:]
+template <typename CT>
+struct LatentPostP {
+  const float* D; long ldd;
+  const bf16 *wq, *wkv;
+  float eps;
+  float* cq; long ldq;
+  CT* cache; long slot_stride, tok_stride;   // elements
+  const int *slot, *pos;
+  const float2* cs;                          // [T][rot_dims/2]
+  int q_rank, kv_rank, rot_dim, rot_dims, own_kv;
+};
+template <typename CT>
+__global__ void latent_post_kernel(LatentPostP<CT> p) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const float* d = p.D + (long)t * p.ldd;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) ss += d[i] * d[i];
+  float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)p.q_rank + p.eps);
+  for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) p.cq[(long)t * p.ldq + i] = d[i] * inv * bf2f(p.wq[i]);
+  if (!p.own_kv) return;
+  const float* k = d + p.q_rank;
+  ss = 0.f;
+  for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) ss += k[i] * k[i];
+  inv = 1.0f / sqrtf(block_sum(ss, red) / (float)p.kv_rank + p.eps);
+  CT* c = p.cache + (long)p.slot[t] * p.slot_stride + (long)p.pos[t] * p.tok_stride;
+  for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) st_act(c + i, k[i] * inv * bf2f(p.wkv[i]));
+  const float* r = k + p.kv_rank;
+  const int half = p.rot_dims / 2;
+  for (int i = threadIdx.x; i < p.rot_dim; i += blockDim.x) {
+    float v;
+    if (i < half) {
+      const float2 a = p.cs[(long)t * half + i];
+      v = r[i] * a.x - r[i + half] * a.y;
+    } else if (i < p.rot_dims) {
+      const float2 a = p.cs[(long)t * half + i - half];
+      v = r[i] * a.x + r[i - half] * a.y;
+    } else {
+      v = r[i];
+    }
+    st_act(c + p.kv_rank + i, v);
+  }
+}
+
+// rotated query parts into the absorbed query rows: qa[t][h][kv_rank + i] = rope(q[t][h][dim + i])
+__global__ void rope_q_kernel(const float* __restrict__ q, long ldq, int qh_stride, int dim, float* __restrict__ qa,
+                              long ldqa, int Dl, int kv_rank, const float2* __restrict__ cs, int H, int rot_dim,
+                              int rot_dims) {
+  const int t = blockIdx.x, half = rot_dims / 2;
+  for (int e = threadIdx.x; e < H * rot_dim; e += blockDim.x) {
+    const int h = e / rot_dim, i = e % rot_dim;
+    const float* r = q + (long)t * ldq + (long)h * qh_stride + dim;
+    float v;
+    if (i < half) {
+      const float2 a = cs[(long)t * half + i];
+      v = r[i] * a.x - r[i + half] * a.y;
+    } else if (i < rot_dims) {
+      const float2 a = cs[(long)t * half + i - half];
+      v = r[i] * a.x + r[i - half] * a.y;
+    } else {
+      v = r[i];
+    }
+    qa[(long)t * ldqa + (long)h * Dl + kv_rank + i] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// absorbed latent attention.  Block = (query token, group of up to 8 heads); a warp per head.  Keys are the cache
+// rows 0..pos[t] of slot[t], staged 32 at a time in shared memory (fp32); lane j scores key j, then the lanes
+// share the probabilities and each lane accumulates its columns of the latent sum (online softmax, fp32).
+constexpr int LA_KT = 32;
+template <typename CT>
+struct LatAttnP {
+  const float* qa; long ldqa;            // [T][H][Dl]
+  const CT* cache; long slot_stride, tok_stride;
+  const int *slot, *pos;
+  float* out; long ldo;                  // [T][H][kv_rank]
+  int H, Dl, kv_rank;
+  float scale;
+  int round_q;                           // bf16 serving mode: the query operand is rounded like the keys
+};
+template <typename CT>
+__global__ void latent_attention_kernel(LatAttnP<CT> p) {
+  extern __shared__ float sm[];
+  const int t = blockIdx.x, hg = blockIdx.y, nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int Dl = p.Dl, ldk = Dl + 1;
+  float* keys = sm;                       // [LA_KT][Dl + 1]
+  float* qs = sm + LA_KT * ldk;           // [nw][Dl]
+  const int h = hg * nw + warp;
+  const bool live = h < p.H;
+  if (live) {
+    const float* q = p.qa + (long)t * p.ldqa + (long)h * Dl;
+    for (int i = lane; i < Dl; i += 32) qs[warp * Dl + i] = p.round_q ? rbf(q[i]) : q[i];
+  }
+  const int n_keys = p.pos[t] + 1;
+  const CT* base = p.cache + (long)p.slot[t] * p.slot_stride;
+  const int per_lane = (p.kv_rank + 31) / 32;
+  float m = -INFINITY, l = 0.f;
+  float acc[32];                          // kv_rank <= 1024
+#pragma unroll
+  for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+  for (int k0 = 0; k0 < n_keys; k0 += LA_KT) {
+    const int nk = min(LA_KT, n_keys - k0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nk * Dl; e += blockDim.x) {
+      const int j = e / Dl, i = e % Dl;
+      keys[j * ldk + i] = ld_act(base + (long)(k0 + j) * p.tok_stride + i);
+    }
+    __syncthreads();
+    if (!live) continue;
+    float s = -INFINITY;
+    if (lane < nk) {
+      const float* kr = keys + lane * ldk;
+      const float* qr = qs + warp * Dl;
+      float a = 0.f;
+      for (int i = 0; i < Dl; ++i) a = fmaf(qr[i], kr[i], a);
+      s = a * p.scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);     // first tile: exp(-inf) = 0
+    const float pj = lane < nk ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(pj);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < per_lane) acc[i] *= corr;
+    for (int j = 0; j < nk; ++j) {
+      const float w = __shfl_sync(0xffffffffu, pj, j);
+      const float* kr = keys + j * ldk;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < per_lane) {
+          const int d = lane + 32 * i;
+          if (d < p.kv_rank) acc[i] = fmaf(w, kr[d], acc[i]);
+        }
+    }
+  }
+  if (!live) return;
+  const float inv = 1.0f / l;
+  float* o = p.out + (long)t * p.ldo + (long)h * p.kv_rank;
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    if (i < per_lane) {
+      const int d = lane + 32 * i;
+      if (d < p.kv_rank) o[d] = acc[i] * inv;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// router: z[t][E] fp32 -> the `top` largest (lowest index wins a tie), weights = softmax over the chosen logits
+__global__ void router_topk_kernel(const float* __restrict__ z, long ldz, int E, int top, int* __restrict__ idx,
+                                   float* __restrict__ wgt, int T) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float* zr = z + (long)t * ldz;
+  unsigned long long taken_lo = 0;        // lanes own experts lane, lane+32, ...: up to 64 per lane (E <= 2048)
+  float vmax = 0.f, denom = 0.f;
+  for (int s = 0; s < top; ++s) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane, n = 0; e < E; e += 32, ++n) {
+      if ((taken_lo >> n) & 1ull) continue;
+      const float v = zr[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if ((bi & 31) == lane && bi < E) taken_lo |= 1ull << (bi >> 5);
+    if (s == 0) vmax = best;
+    const float e = expf(best - vmax);
+    denom += e;
+    if (lane == 0) { idx[(long)t * top + s] = bi; wgt[(long)t * top + s] = e; }
+  }
+  __syncwarp();
+  if (lane == 0)
+    for (int s = 0; s < top; ++s) wgt[(long)t * top + s] /= denom;
+}
+
+// group the (token, choice) entries by expert: list[e][0..count[e]) = entry numbers in ascending order
+__global__ void moe_group_kernel(const int* __restrict__ idx, int n_entries, int* __restrict__ list, long list_stride,
+                                 int* __restrict__ count) {
+  __shared__ int warp_tot[32];
+  __shared__ int base;
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (threadIdx.x == 0) base = 0;
+  __syncthreads();
+  for (int i0 = 0; i0 < n_entries; i0 += blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    const bool hit = i < n_entries && idx[i] == e;
+    const unsigned b = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) warp_tot[warp] = __popc(b);
+    __syncthreads();
+    int off = base;
+    for (int w = 0; w < warp; ++w) off += warp_tot[w];
+    if (hit) list[(long)e * list_stride + off + __popc(b & ((1u << lane) - 1))] = i;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int w = 0; w < nw; ++w) tot += warp_tot[w];
+      base += tot;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) count[e] = base;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// general row GEMM  Y[b][r][n] = epi( sum_k X[b][xr][k] * W[b][n][k] + bias[n] )
+struct GemmRowsP {
+  const float* X; long ldx, xb;          // row pitch, batch stride (elements)
+  const bf16* W; long ldw, wb;
+  const bf16* bias;
+  float* Y; long ldy, yb;
+  const int* list; long list_stride;     // per batch: entry numbers; x row = entry / x_div, y row = entry
+  const int* count;                      // per batch: rows (device); NULL: M rows, no list
+  int x_div;
+  int M, N, K;
+  int epi; float epi_param;              // 0 none, 1 relu^2, 2 param * tanh(v / param)
+  int round_x;
+};
+__device__ __forceinline__ float gemm_epi(float v, int epi, float param) {
+  if (epi == 1) { v = fmaxf(v, 0.f); return v * v; }
+  if (epi == 2) return param * tanhf(v / param);
+  return v;
+}
+constexpr int GB_M = 64, GB_N = 64, GB_K = 16;
+__global__ void __launch_bounds__(256) gemm_rows_kernel(GemmRowsP p) {
+  __shared__ float As[GB_K][GB_M + 4];
+  __shared__ float Bs[GB_K][GB_N + 4];
+  __shared__ int xrow[GB_M], yrow[GB_M];
+  const int b = blockIdx.z;
+  const int rows = p.count ? p.count[b] : p.M;
+  const int m0 = blockIdx.y * GB_M, n0 = blockIdx.x * GB_N;
+  if (m0 >= rows) return;
+  const int tid = threadIdx.x;
+  if (tid < GB_M) {
+    const int r = m0 + tid;
+    int xr = -1, yr = -1;
+    if (r < rows) {
+      if (p.list) { const int e = p.list[(long)b * p.list_stride + r]; xr = e / p.x_div; yr = e; }
+      else { xr = yr = r; }
+    }
+    xrow[tid] = xr; yrow[tid] = yr;
+  }
+  __syncthreads();
+  const float* X = p.X + (long)b * p.xb;
+  const bf16* W = p.W + (long)b * p.wb;
+  const int tx = tid & 15, ty = tid >> 4;      // 16 x 16 threads, 4 x 4 outputs each
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < p.K; k0 += GB_K) {
+    // stage 64 x 16 of X and of W: thread -> (row = tid / 4, 4 consecutive k)
+    {
+      const int r = tid >> 2, kk = (tid & 3) * 4;
+      const int xr = xrow[r];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int k = k0 + kk + j;
+        float v = 0.f;
+        if (xr >= 0 && k < p.K) { v = X[(long)xr * p.ldx + k]; if (p.round_x) v = rbf(v); }
+        As[kk + j][r] = v;
+      }
+      const int n = n0 + r;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int k = k0 + kk + j;
+        Bs[kk + j][r] = (n < p.N && k < p.K) ? bf2f(W[(long)n * p.ldw + k]) : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GB_K; ++k) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  float* Y = p.Y + (long)b * p.yb;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int yr = yrow[ty * 4 + i];
+    if (yr < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= p.N) continue;
+      float v = acc[i][j];
+      if (p.bias) v += bf2f(p.bias[n]);
+      Y[(long)yr * p.ldy + n] = gemm_epi(v, p.epi, p.epi_param);
+    }
+  }
+}
+
+// the skinny sibling for decode steps (few rows): a warp per weight row, the rows of X in chunks of 8 per pass
+// over the weight row; k order fixed by the lane striding + butterfly, independent of the other rows
+constexpr int GS_R = 8;
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmRowsP p) {
+  const int b = blockIdx.z;
+  const int rows = p.count ? p.count[b] : p.M;
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (n >= p.N || rows <= 0) return;
+  const float* X = p.X + (long)b * p.xb;
+  const bf16* w = p.W + (long)b * p.wb + (long)n * p.ldw;
+  float* Y = p.Y + (long)b * p.yb;
+  const float bias = p.bias ? bf2f(p.bias[n]) : 0.f;
+  for (int r0 = 0; r0 < rows; r0 += GS_R) {
+    int xr[GS_R], yr[GS_R];
+#pragma unroll
+    for (int i = 0; i < GS_R; ++i) {
+      const int r = r0 + i;
+      xr[i] = yr[i] = -1;
+      if (r < rows) {
+        if (p.list) { const int e = p.list[(long)b * p.list_stride + r]; xr[i] = e / p.x_div; yr[i] = e; }
+        else { xr[i] = yr[i] = r; }
+      }
+    }
+    float acc[GS_R] = {};
+    for (int k = lane; k < p.K; k += 32) {
+      const float wv = bf2f(w[k]);
+#pragma unroll
+      for (int i = 0; i < GS_R; ++i)
+        if (xr[i] >= 0) {
+          float v = X[(long)xr[i] * p.ldx + k];
+          if (p.round_x) v = rbf(v);
+          acc[i] = fmaf(v, wv, acc[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < GS_R; ++i) {
+      const float v = warp_sum(acc[i]);
+      if (lane == 0 && yr[i] >= 0) Y[(long)yr[i] * p.ldy + n] = gemm_epi(v + bias, p.epi, p.epi_param);
+    }
+  }
+}
+
+// greedy pick per row: lowest index of the largest logit, and its log-probability
+__global__ void argmax_rows_kernel(const float* __restrict__ z, long ldz, int V, int* __restrict__ tok,
+                                   float* __restrict__ logprob) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float red[32];
+  const float* r = z + (long)blockIdx.x * ldz;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = r[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  best = sv[0]; bi = si[0];
+  for (int i = 1; i < nw; ++i)
+    if (sv[i] > best || (sv[i] == best && si[i] < bi)) { best = sv[i]; bi = si[i]; }
+  float se = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) se += expf(r[i] - best);
+  const float tot = block_sum(se, red);
+  if (threadIdx.x == 0) {
+    tok[blockIdx.x] = bi;
+    if (logprob) logprob[blockIdx.x] = -logf(tot);
+  }
+}
+
+// decode bookkeeping on the device: the sampled tokens become the next step's inputs, positions advance
+__global__ void advance_rows_kernel(const int* __restrict__ sampled, int* __restrict__ tok, int* __restrict__ pos,
+                                    const int* __restrict__ active, int* __restrict__ log, int log_stride, int step,
+                                    int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  if (log) log[(long)step * log_stride + b] = sampled[b];
+  if (active == nullptr || active[b]) { tok[b] = sampled[b]; pos[b] += 1; }
+}
+
+unsigned long long g_attn_attr_f32 = 0, g_attn_attr_bf16 = 0;
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_lm_embed(const int* tokens, const void* embed, float scale, float* x, int T, int W, int vocab, void* st) {
+  B200_REQUIRE(tokens && embed && x && T > 0 && W > 0, "lm_embed: bad argument");
+  embed_scale_kernel<<<T, 256, 0, (cudaStream_t)st>>>(tokens, (const bf16*)embed, scale, x, W, vocab);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T, int half, void* st) {
+  B200_REQUIRE(pos && inv_freq && cs && T > 0 && half > 0, "lm_rope_table: bad argument");
+  rope_table_kernel<<<cdiv((long)T * half, 256), 256, 0, (cudaStream_t)st>>>(pos, inv_freq, (float2*)cs, T, half);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const void* w, float w_offset, float eps,
+                      float* x, long ldx, int add, const int* rows, int T, int N, void* st) {
+  B200_REQUIRE(y && w && x && T > 0 && N > 0, "lm_norm_rows: bad argument");
+  B200_REQUIRE((N + 32) * 4 <= 48 * 1024, "lm_norm_rows: rows of %d numbers do not fit shared memory", N);
+  NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, x, ldx, add, rows, N};
+  norm_rows_kernel<<<T, 256, (N + 32) * sizeof(float), (cudaStream_t)st>>>(p);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wkv, float eps, float* cq, long ldq,
+                        void* cache, int cache_bf16, long slot_stride, long tok_stride, const int* slot,
+                        const int* pos, const float* cs, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                        int own_kv, int T, void* st) {
+  B200_REQUIRE(D && wq && cq && T > 0, "lm_latent_post: bad argument");
+  B200_REQUIRE(!own_kv || (wkv && cache && slot && pos && cs), "lm_latent_post: a layer with its own latent needs a cache");
+  B200_REQUIRE(rot_dims % 2 == 0 && rot_dims <= rot_dim, "lm_latent_post: rotated dims %d of %d", rot_dims, rot_dim);
+  if (cache_bf16) {
+    LatentPostP<bf16> p{D, ldd, (const bf16*)wq, (const bf16*)wkv, eps, cq, ldq, (bf16*)cache, slot_stride, tok_stride,
+                        slot, pos, (const float2*)cs, q_rank, kv_rank, rot_dim, rot_dims, own_kv};
+    latent_post_kernel<bf16><<<T, 128, 0, (cudaStream_t)st>>>(p);
+  } else {
+    LatentPostP<float> p{D, ldd, (const bf16*)wq, (const bf16*)wkv, eps, cq, ldq, (float*)cache, slot_stride,
+                         tok_stride, slot, pos, (const float2*)cs, q_rank, kv_rank, rot_dim, rot_dims, own_kv};
+    latent_post_kernel<float><<<T, 128, 0, (cudaStream_t)st>>>(p);
+  }
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_rope_q(const float* q, long ldq, int qh_stride, int dim, float* qa, long ldqa, int Dl, int kv_rank,
+                   const float* cs, int H, int rot_dim, int rot_dims, int T, void* st) {
+  B200_REQUIRE(q && qa && cs && T > 0, "lm_rope_q: bad argument");
+  rope_q_kernel<<<T, 128, 0, (cudaStream_t)st>>>(q, ldq, qh_stride, dim, qa, ldqa, Dl, kv_rank, (const float2*)cs, H,
+                                                 rot_dim, rot_dims);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int cache_bf16, long slot_stride,
+                             long tok_stride, const int* slot, const int* pos, float* out, long ldo, int H, int Dl,
+                             int kv_rank, float scale, int round_q, int T, void* st) {
+  B200_REQUIRE(qa && cache && slot && pos && out && T > 0 && H > 0, "lm_latent_attention: bad argument");
+  B200_REQUIRE(kv_rank <= 1024 && kv_rank <= Dl, "lm_latent_attention: latent rank %d not supported", kv_rank);
+  const int nw = H < 8 ? H : 8;
+  const size_t smem = ((size_t)LA_KT * (Dl + 1) + (size_t)nw * Dl) * sizeof(float);
+  B200_REQUIRE(smem <= 200 * 1024, "lm_latent_attention: rows of %d numbers do not fit shared memory", Dl);
+  dim3 grid(T, cdiv(H, nw));
+  if (cache_bf16) {
+    if (first_use_on_device(&g_attn_attr_bf16))
+      B200_CUDA(cudaFuncSetAttribute(latent_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    LatAttnP<bf16> p{qa, ldqa, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q};
+    latent_attention_kernel<bf16><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
+  } else {
+    if (first_use_on_device(&g_attn_attr_f32))
+      B200_CUDA(cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    LatAttnP<float> p{qa, ldqa, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q};
+    latent_attention_kernel<float><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
+  }
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_router_topk(const float* z, long ldz, int E, int top, int* idx, float* wgt, int T, void* st) {
+  B200_REQUIRE(z && idx && wgt && T > 0 && top > 0 && top <= E && E <= 2048, "lm_router_topk: bad argument");
+  router_topk_kernel<<<cdiv(T, 4), 128, 0, (cudaStream_t)st>>>(z, ldz, E, top, idx, wgt, T);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_moe_group(const int* idx, int n_entries, int E, int* list, long list_stride, int* count, void* st) {
+  B200_REQUIRE(idx && list && count && n_entries > 0 && E > 0, "lm_moe_group: bad argument");
+  moe_group_kernel<<<E, 256, 0, (cudaStream_t)st>>>(idx, n_entries, list, list_stride, count);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw, long wb, const void* bias, float* Y,
+                      long ldy, long yb, const int* list, long list_stride, const int* count, int x_div, int M, int N,
+                      int K, int batch, int epi, float epi_param, int round_x, int skinny, void* st) {
+  B200_REQUIRE(X && W && Y && M > 0 && N > 0 && K > 0 && batch > 0, "lm_gemm_rows: bad argument");
+  B200_REQUIRE((list == nullptr) == (count == nullptr), "lm_gemm_rows: a row list needs its counts");
+  GemmRowsP p{X, ldx, xb, (const bf16*)W, ldw, wb, (const bf16*)bias, Y, ldy, yb, list, list_stride, count,
+              x_div > 0 ? x_div : 1, M, N, K, epi, epi_param, round_x};
+  if (skinny) {
+    dim3 grid(cdiv(N, 8), 1, batch);
+    gemm_skinny_kernel<<<grid, 256, 0, (cudaStream_t)st>>>(p);
+  } else {
+    dim3 grid(cdiv(N, GB_N), cdiv(M, GB_M), batch);
+    gemm_rows_kernel<<<grid, 256, 0, (cudaStream_t)st>>>(p);
+  }
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_argmax_rows(const float* z, long ldz, int V, int* tok, float* logprob, int B, void* st) {
+  B200_REQUIRE(z && tok && B > 0 && V > 0, "lm_argmax_rows: bad argument");
+  argmax_rows_kernel<<<B, 256, 0, (cudaStream_t)st>>>(z, ldz, V, tok, logprob);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* active, int* log, int log_stride, int step,
+                         int B, void* st) {
+  B200_REQUIRE(sampled && tok && pos && B > 0, "lm_advance_rows: bad argument");
+  advance_rows_kernel<<<cdiv(B, 128), 128, 0, (cudaStream_t)st>>>(sampled, tok, pos, active, log, log_stride, step, B);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+}  // extern "C"

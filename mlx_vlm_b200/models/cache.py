@@ -36,14 +36,87 @@ class KVPool:
         if n_tokens <= self.capacity:
             return False
         cap = ((max(n_tokens, 2 * self.capacity) + self.step - 1) // self.step) * self.step
-        new = torch.zeros((self.n_layers, 2, self.batch, self.n_kv, cap, self.hd),
-                          dtype=self.dtype, device=self.device)
+        new = torch.zeros(self._shape(cap), dtype=self.dtype, device=self.device)
         if self.buf is not None and live_tokens > 0:
             new[..., :live_tokens, :].copy_(self.buf[..., :live_tokens, :])
         self.buf = new
         self.capacity = cap
         self.generation += 1
         return True
+
+
+    def _shape(self, cap: int):
+        return (self.n_layers, 2, self.batch, self.n_kv, cap, self.hd)
+
+
+class LatentPool(KVPool):
+    """Pool of a latent-attention model: ONE row of `row_dim` numbers per token and caching layer — the normed
+    key/value latent followed by the rotated key part that all heads share — laid out (caching layers, slots,
+    capacity, row_dim), bf16 when serving, fp32 in the exact mode.  A slot is the cache of one request; the
+    kernels address (slot, position) per token, so requests of any length share a launch."""
+
+    def __init__(self, n_layers: int, row_dim: int, device, batch: int = 1, capacity: int = 0, dtype=torch.bfloat16):
+        super().__init__(n_layers, 1, row_dim, device, batch=batch, capacity=capacity, dtype=dtype)
+
+    def _shape(self, cap: int):
+        return (self.n_layers, self.batch, cap, self.hd)
+
+    def add_slots(self, batch: int, live_tokens: int):
+        """more slots (a re-allocation that keeps the first `live_tokens` positions of every slot)"""
+        if batch <= self.batch:
+            return False
+        old, self.batch = self.buf, batch
+        self.buf = torch.zeros(self._shape(self.capacity), dtype=self.dtype, device=self.device)
+        if old is not None and live_tokens > 0:
+            self.buf[:, :old.shape[1], :live_tokens].copy_(old[:, :, :live_tokens])
+        self.generation += 1
+        return True
+
+    def copy_slot(self, dst: int, src_pool: "LatentPool", src: int, n_tokens: int):
+        if n_tokens > 0:
+            self.buf[:, dst, :n_tokens].copy_(src_pool.buf[:, src, :n_tokens])
+
+
+class SlotTable:
+    """Which slots of a pool are in use: the lowest free slot is handed out first, a released slot is
+    used again by the next request."""
+
+    def __init__(self, n_slots: int = 0):
+        self.n_slots = n_slots
+        self._free: List[int] = list(range(n_slots))
+        self._used: dict = {}
+
+    def grow(self, n_slots: int):
+        self._free.extend(range(self.n_slots, n_slots))
+        self.n_slots = max(self.n_slots, n_slots)
+
+    @property
+    def free(self) -> int:
+        return len(self._free)
+
+    def acquire(self, owner) -> int:
+        if owner in self._used:
+            raise KeyError(f"{owner!r} already holds slot {self._used[owner]}")
+        if not self._free:
+            raise RuntimeError("no free slot")
+        self._free.sort()
+        slot = self._free.pop(0)
+        self._used[owner] = slot
+        return slot
+
+    def release(self, owner) -> int:
+        slot = self._used.pop(owner)
+        self._free.append(slot)
+        return slot
+
+    def slot_of(self, owner) -> int:
+        return self._used[owner]
+
+    def __contains__(self, owner) -> bool:
+        return owner in self._used
+
+    def __len__(self) -> int:
+        return len(self._used)
 
 
 class _BaseCache:
@@ -168,6 +241,54 @@ class KVCache(_BaseCache):
         if k is None:
             return 0
         return 2 * k.numel() * k.element_size()
+
+
+class LatentCache(_BaseCache):
+    """One layer's view of a `LatentPool` slot, with the `KVCache` surface the generation loops use (`offset`,
+    `trim`, `size`, `state`, `is_trimmable`).  `keys` are the cached rows [latent | rotated key part]; `values`
+    are the latent columns of the same rows (a latent row is key and value at once).  A layer that borrows
+    another layer's latent holds a view with `shared=True` on that layer's rows: it reads them and never writes."""
+
+    def __init__(self, pool: LatentPool, layer: int, row: int = 0, latent_dim: Optional[int] = None, shared: bool = False):
+        self._pool, self._layer, self._row = pool, layer, row
+        self._latent = pool.hd if latent_dim is None else latent_dim
+        self.shared = shared
+        self.offset = 0
+
+    @property
+    def keys(self):
+        return None if self._pool.buf is None else self._pool.buf[self._layer, self._row:self._row + 1]
+
+    @property
+    def values(self):
+        k = self.keys
+        return None if k is None else k[..., :self._latent]
+
+    @property
+    def state(self):
+        return self.keys[:, :self.offset], self.values[:, :self.offset]
+
+    def size(self):
+        return self.offset
+
+    def is_trimmable(self):
+        return True
+
+    def trim(self, n):
+        n = min(self.offset, n)
+        self.offset -= n
+        return n
+
+    def empty(self):
+        return self.offset == 0
+
+    def make_mask(self, N: int, return_array: bool = False, window_size=None):
+        return None if N == 1 else "causal"
+
+    @property
+    def nbytes(self):
+        k = self.keys
+        return 0 if k is None or self.shared else k.numel() * k.element_size()
 
 
 def make_prompt_cache(model: Any, max_kv_size: Optional[int] = None) -> List[Any]:

@@ -1,0 +1,144 @@
+"""Thin Python face of the layer-level ops (csrc/layer_ops.cu) — the sibling of tower_ops.py for decoder
+layers that are assembled on the host: fp32 residual stream, norms on the sublayer's output, latent
+attention over (slot, position)-addressed cache rows, rotate-half rotary, expert mixtures, row GEMMs.
+
+Every call enqueues one kernel on the engine's stream.  torch is the memory container only.
+`exact=True` is the true-fp32 mode (fp32 cache rows, no rounding of matrix operands); otherwise cache rows
+are bf16 and the operands of the matrix products are rounded to bf16 on load (fp32 accumulation).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import _native as N
+
+EPI_NONE, EPI_RELU2, EPI_SOFTCAP = 0, 1, 2
+SKINNY_ROWS = 16      # up to this many rows a product runs on the warp-per-weight-row kernel
+
+
+class LayerOps:
+    def __init__(self, device, stream: torch.cuda.Stream, exact: bool = False):
+        if torch.device(device).type != "cuda":
+            raise N.B200Error("the layer ops need a CUDA (sm_100a) device; there is no CPU fallback")
+        self.lib = N.lm_lib()
+        self.device, self.stream, self.exact = torch.device(device), stream, bool(exact)
+        self.launches = 0
+        self._inv_freq = {}
+
+    @property
+    def s(self) -> int:
+        return self.stream.cuda_stream
+
+    @property
+    def cache_dtype(self):
+        return torch.float32 if self.exact else torch.bfloat16
+
+    def _ok(self, rc, what):
+        self.launches += 1
+        N.check(rc, what, self.lib)
+
+    def empty(self, shape, dtype=torch.float32) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            return torch.empty(shape, dtype=dtype, device=self.device)
+
+    def to_device(self, arr, dtype=np.int32) -> torch.Tensor:
+        t = torch.from_numpy(np.ascontiguousarray(arr, dtype=dtype)).pin_memory()
+        with torch.cuda.stream(self.stream):
+            return t.to(self.device, non_blocking=True)
+
+    # ------------------------------------------------------------------------------------------
+    def embed(self, tokens: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+        T, (V, W) = tokens.shape[0], table.shape
+        x = self.empty((T, W))
+        self._ok(self.lib.b200_lm_embed(tokens.data_ptr(), table.data_ptr(), float(scale), x.data_ptr(), T, W, V,
+                                        self.s), "lm_embed")
+        return x
+
+    def inv_freq(self, base: float, dims: int) -> torch.Tensor:
+        """f_i = base^(-2i/dims), i < dims/2, computed in double precision on the host (once per rotation)"""
+        key = (float(base), int(dims))
+        if key not in self._inv_freq:
+            f = np.power(np.float64(base), -2.0 * np.arange(dims // 2, dtype=np.float64) / dims)
+            self._inv_freq[key] = self.to_device(f, np.float64)
+        return self._inv_freq[key]
+
+    def rope_table(self, pos: torch.Tensor, base: float, dims: int) -> torch.Tensor:
+        T, half = pos.shape[0], dims // 2
+        cs = self.empty((T, half, 2))
+        self._ok(self.lib.b200_lm_rope_table(pos.data_ptr(), self.inv_freq(base, dims).data_ptr(), cs.data_ptr(), T,
+                                             half, self.s), "lm_rope_table")
+        return cs
+
+    def norm_rows(self, y: torch.Tensor, w: torch.Tensor, eps: float, x: torch.Tensor, *, w_offset: float = 0.0,
+                  add: bool = False, combine: Optional[torch.Tensor] = None, top: int = 0,
+                  rows: Optional[torch.Tensor] = None):
+        """x (T, N) = or += rmsnorm(y rows) * (w_offset + w); `combine` (T, top): y holds `top` rows per token"""
+        T, n = x.shape
+        self._ok(self.lib.b200_lm_norm_rows(y.data_ptr(), y.stride(0), N.ptr(combine), int(top), w.data_ptr(),
+                                            float(w_offset), float(eps), x.data_ptr(), x.stride(0), int(add),
+                                            N.ptr(rows), T, n, self.s), "lm_norm_rows")
+
+    def latent_post(self, D, wq, wkv, eps, cq, cache_layer, slot, pos, cs, q_rank, kv_rank, rot_dim, rot_dims):
+        """cache_layer: (slots, capacity, kv_rank + rot_dim) view of the pool, or None for a layer that borrows"""
+        own = cache_layer is not None
+        self._ok(self.lib.b200_lm_latent_post(
+            D.data_ptr(), D.stride(0), wq.data_ptr(), N.ptr(wkv), float(eps), cq.data_ptr(), cq.stride(0),
+            N.ptr(cache_layer), int(own and cache_layer.dtype == torch.bfloat16),
+            cache_layer.stride(0) if own else 0, cache_layer.stride(1) if own else 0, N.ptr(slot), N.ptr(pos),
+            N.ptr(cs), q_rank, kv_rank, rot_dim, rot_dims, int(own), D.shape[0], self.s), "lm_latent_post")
+
+    def rope_q(self, q, qa, cs, H, dim, rot_dim, rot_dims, kv_rank):
+        T = q.shape[0]
+        self._ok(self.lib.b200_lm_rope_q(q.data_ptr(), q.stride(0), dim + rot_dim, dim, qa.data_ptr(), qa.stride(0),
+                                         kv_rank + rot_dim, kv_rank, cs.data_ptr(), H, rot_dim, rot_dims, T, self.s),
+                 "lm_rope_q")
+
+    def latent_attention(self, qa, cache_layer, slot, pos, out, H, kv_rank, scale):
+        T, Dl = qa.shape[0], cache_layer.shape[-1]
+        self._ok(self.lib.b200_lm_latent_attention(
+            qa.data_ptr(), qa.stride(0), cache_layer.data_ptr(), int(cache_layer.dtype == torch.bfloat16),
+            cache_layer.stride(0), cache_layer.stride(1), slot.data_ptr(), pos.data_ptr(), out.data_ptr(),
+            out.stride(0), H, Dl, kv_rank, float(scale), 0, T, self.s), "lm_latent_attention")
+
+    def router_topk(self, z, top):
+        T, E = z.shape
+        idx, wgt = self.empty((T, top), torch.int32), self.empty((T, top))
+        self._ok(self.lib.b200_lm_router_topk(z.data_ptr(), z.stride(0), E, top, idx.data_ptr(), wgt.data_ptr(), T,
+                                              self.s), "lm_router_topk")
+        return idx, wgt
+
+    def moe_group(self, idx, E):
+        T, top = idx.shape
+        lists, count = self.empty((E, T), torch.int32), self.empty((E,), torch.int32)
+        self._ok(self.lib.b200_lm_moe_group(idx.data_ptr(), T * top, E, lists.data_ptr(), T, count.data_ptr(), self.s),
+                 "lm_moe_group")
+        return lists, count
+
+    def gemm(self, X, W, Y, *, M, N_, K, ldx=None, xb=0, ldw=None, wb=0, ldy=None, yb=0, batch=1, bias=None,
+             lists=None, count=None, x_div=1, epi=EPI_NONE, epi_param=0.0):
+        """Y[b][r][:] = epi(X[b][r'] . W[b]^T + bias); strides in elements (default: the tensors' own rows)"""
+        self._ok(self.lib.b200_lm_gemm_rows(
+            X.data_ptr(), X.stride(0) if ldx is None else ldx, xb, W.data_ptr(), K if ldw is None else ldw, wb,
+            N.ptr(bias), Y.data_ptr(), Y.stride(0) if ldy is None else ldy, yb, N.ptr(lists),
+            lists.stride(0) if lists is not None else 0, N.ptr(count), x_div, M, N_, K, batch, epi, float(epi_param),
+            int(not self.exact), int(M <= SKINNY_ROWS), self.s), "lm_gemm_rows")
+
+    def linear(self, X: torch.Tensor, W: torch.Tensor, bias=None, epi=EPI_NONE, epi_param=0.0) -> torch.Tensor:
+        (T, K), n = X.shape, W.shape[0]
+        Y = self.empty((T, n))
+        self.gemm(X, W, Y, M=T, N_=n, K=K, bias=bias, epi=epi, epi_param=epi_param)
+        return Y
+
+    def argmax_rows(self, z, tok, logprob=None):
+        B, V = z.shape
+        self._ok(self.lib.b200_lm_argmax_rows(z.data_ptr(), z.stride(0), V, tok.data_ptr(), N.ptr(logprob), B, self.s),
+                 "lm_argmax_rows")
+
+    def advance_rows(self, sampled, tok, pos, active=None, log=None, step=0):
+        B = tok.shape[0]
+        self._ok(self.lib.b200_lm_advance_rows(sampled.data_ptr(), tok.data_ptr(), pos.data_ptr(), N.ptr(active),
+                                               N.ptr(log), log.stride(0) if log is not None else 0, int(step), B,
+                                               self.s), "lm_advance_rows")

@@ -26,7 +26,11 @@ MODEL_REMAPPING: Dict[str, str] = {}
 
 def get_model_and_args(config: dict):
     """utils.py:588-635: import mlx_vlm_b200.models.<model_type>."""
-    model_type = MODEL_REMAPPING.get(config["model_type"].lower(), config["model_type"].lower())
+    # the class is named by `model_type`, or by `architecture` in checkpoints that carry no model_type
+    name = (config.get("model_type") or config.get("architecture") or "").lower()
+    if not name:
+        raise ValueError("config.json names neither `model_type` nor `architecture`")
+    model_type = MODEL_REMAPPING.get(name, name)
     try:
         arch = importlib.import_module(f"mlx_vlm_b200.models.{model_type}")
     except ImportError as e:
@@ -66,7 +70,8 @@ def load_model(model_path: str, lazy: bool = False, strict: bool = True, device=
         raise FileNotFoundError(f"No safetensors found in {model_path}")
     arch, _ = get_model_and_args(config)
     model_config = arch.ModelConfig.from_dict(config)
-    model = arch.Model(model_config, device=device)
+    extra = {"dtype": kwargs["dtype"]} if kwargs.get("dtype") is not None else {}   # models with an exact mode
+    model = arch.Model(model_config, device=device, **extra)
     weights: Dict[str, torch.Tensor] = {}
     for fpath in files:
         weights.update(_read_safetensors(fpath))
