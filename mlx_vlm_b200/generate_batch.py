@@ -389,8 +389,11 @@ class BatchGenerator:
         step = cache_mod.KVPool.step
         cap = ((need_tokens + step - 1) // step) * step
         if self._pool is None:
-            self._pool = cache_mod.KVPool(lm.args.num_hidden_layers, lm.n_kv_heads, lm.head_dim, eng.device,
-                                          batch=self.completion_batch_size, capacity=cap)
+            if hasattr(lm, "make_pool"):     # the model brings its own cache layout (e.g. latent rows)
+                self._pool = lm.make_pool(self.completion_batch_size, cap)
+            else:
+                self._pool = cache_mod.KVPool(lm.args.num_hidden_layers, lm.n_kv_heads, lm.head_dim, eng.device,
+                                              batch=self.completion_batch_size, capacity=cap)
         elif cap > self._pool.capacity:
             import contextlib
             eng.stream.synchronize()

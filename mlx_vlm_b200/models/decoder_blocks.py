@@ -195,6 +195,8 @@ def assign_cache_layers(layers: List[PostNormLayer]) -> int:
     for L in layers:
         m = L.mixer
         if not m.own_kv:
+            if not 0 <= m.kv_from < m.index:
+                raise ValueError(f"layer {m.index} borrows the latent of layer {m.kv_from}, which does not run before it")
             src = layers[m.kv_from].mixer
             if not src.own_kv or (src.kv_rank, src.rot_dim, src.rot_base, src.rot_dims) != \
                     (m.kv_rank, m.rot_dim, m.rot_base, m.rot_dims):
