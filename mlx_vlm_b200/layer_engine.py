@@ -142,7 +142,7 @@ class LayerEngine:
             self._logits = logits
             self.ops.argmax_rows(logits, self._sampled[:1], self._lp[:1])
             i = self.tokens_launched % self.TOKEN_LOG
-            self.ops.advance_rows(self._sampled[:1], self._tok, self._pos, None, self._log[i:i + 1], 1, 0)
+            self.ops.advance_rows(self._sampled[:1], self._tok, self._pos, None, self._log[i:i + 1], 0)
             self.tokens_launched += 1
 
     def fetch_tokens(self, start: int, n: int, host: torch.Tensor):
@@ -171,8 +171,7 @@ class LayerEngine:
             logits = self.forward(self._tok, self._slot, self._pos)
             self._logits = logits
             self.ops.argmax_rows(logits, self._sampled[:B], self._blp[self._bstep, :B])
-            self.ops.advance_rows(self._sampled[:B], self._tok, self._pos, self._active, self._blog, self.BATCH_LOG_ROWS,
-                                  self._bstep)
+            self.ops.advance_rows(self._sampled[:B], self._tok, self._pos, self._active, self._blog, self._bstep)
             self._bstep += 1
 
     def batch_fetch(self, first_step: int, n_steps: int, tok_host: torch.Tensor, lp_host: Optional[torch.Tensor] = None):
