@@ -510,6 +510,140 @@ def c4_leg(dev, args):
     return out
 
 
+# ------------------------------------------------------------------------------------------------------------
+# `--design buzopel`: prefill and decode throughput of the Buzopel design (latent attention + expert mixture,
+# assembled from decoder_blocks over the layer ops) at sizes that resemble real layers, beside the closest
+# existing model of the package — the Qwen2-VL language model (dense GQA decoder on the native engine) — at equal
+# width, depth, head count and ACTIVE feed-forward size.  Random weights; inputs are token ids resident on the host;
+# CUDA events on the engine's stream; the weights of either model (>= 1 GB) exceed the L2.
+DESIGN_SIZES = {
+    "2048w": dict(width=2048, layers=4, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, experts=64,
+                  top=6, ff=1408, vocab=32000),
+    "4096w": dict(width=4096, layers=4, heads=32, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, experts=64,
+                  top=8, ff=2048, vocab=32000),
+}
+
+
+def _buzopel_config(z):
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+             "q_rank": z["q_rank"], "rot": {"base": 10000.0, "dims": z["rot"]},
+             "scale": 1.0 / float(z["dim"] + z["rot"]) ** 0.5}
+    mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["ff"]}}
+    layers = [{"type": "latent_attention", "mixer": dict(mixer), "mlp": mlp} for _ in range(z["layers"])]
+    for i in range(z["layers"] // 2, z["layers"]):            # the second half borrows the latent of one layer
+        layers[i]["mixer"]["kv_from"] = z["layers"] // 2 - 1
+    return {"architecture": "Buzopel", "vocab": z["vocab"], "width": z["width"], "layers": layers,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "logit_softcap": 30.0}
+
+
+def design_leg(dev, args):
+    import numpy as np
+    import torch
+    from mlx_vlm_b200.models.buzopel import Model as BModel, ModelConfig as BConfig
+    from mlx_vlm_b200.models.cache import make_prompt_cache
+    from mlx_vlm_b200.models.qwen2_vl.config import ModelConfig as QConfig, TextConfig, VisionConfig
+    from mlx_vlm_b200.utils import load_synthetic
+    T, n_dec, rows = args.design_prompt, args.design_out, args.design_rows
+    hbm, hbm_src = _peaks()
+    tpk, tpk_src = _tensor_peak()
+    out = {"prompt_tokens": T, "decode_tokens": n_dec, "rows": rows, "sizes": {}, "peaks": {"hbm_GBs": hbm, "hbm_source": hbm_src,
+           "tensor_TFs": tpk, "tensor_source": tpk_src}}
+    rng = np.random.default_rng(0)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+
+    def timed(eng, fn):
+        for _ in range(args.warmup):
+            fn()
+        eng.stream.synchronize()
+        ev[0].record(eng.stream)
+        for _ in range(args.steps):
+            fn()
+        ev[1].record(eng.stream)
+        eng.stream.synchronize()
+        return ev[0].elapsed_time(ev[1]) / args.steps
+
+    for name, z in DESIGN_SIZES.items():
+        if args.design_sizes and name not in args.design_sizes.split(","):
+            continue
+        ids = rng.integers(0, z["vocab"], size=(1, T))
+        res = {}
+        # ---- the new design ------------------------------------------------------------------------------
+        m = BModel(BConfig.from_dict(_buzopel_config(z)), device=dev).init_random(0)
+        lm, eng = m.language_model, m.engine
+        state = {}
+
+        def b_prefill():
+            state["cache"] = lm.make_cache()
+            lm(ids, cache=state["cache"], logits_to_keep=1, reserve_tokens=T + n_dec * (args.warmup + args.steps + 2))
+
+        def b_decode():
+            lm.fused_greedy_decode_n(n_dec, state["cache"])
+
+        pre = timed(eng, b_prefill)
+        dec = timed(eng, b_decode) / n_dec
+        pool = lm.make_pool(rows, T + n_dec * (args.warmup + args.steps + 2) + 8)
+        caches = [lm.make_cache_row(pool, r) for r in range(rows)]
+        lm.prefill_rows([ids[0]] * rows, [None] * rows, caches)
+        eng.bind_pool(pool)
+        eng.batch_begin([1] * rows, [T] * rows, [T] * rows, [1] * rows)
+        bdec = timed(eng, lambda: eng.batch_decode(n_dec)) / n_dec
+        mx, ff = m.layers[0].mixer, m.layers[0].ff
+        act_w = sum((2 * L.mixer.q_rank * z["width"] + (L.mixer.row_dim * z["width"] if L.mixer.own_kv else 0)
+                     + L.mixer.H * (L.mixer.dim + L.mixer.rot_dim) * L.mixer.q_rank + L.mixer.H * L.mixer.dim * L.mixer.kv_rank
+                     + L.mixer.H * L.mixer.vdim * L.mixer.kv_rank + z["width"] * L.mixer.H * L.mixer.vdim
+                     + L.ff.E * z["width"] + 2 * L.ff.top * L.ff.ff * z["width"]) for L in m.layers) \
+            - sum(L.mixer.q_rank * z["width"] for L in m.layers)
+        head_w = z["vocab"] * z["width"]
+        bytes_tok = 2 * (act_w + head_w)                                   # bf16 weights one decoded token touches
+        flops_tok = 2 * (act_w + head_w / T)                               # prefill: the head runs on one row
+        att_flops = sum(2 * L.mixer.H * (L.mixer.row_dim + L.mixer.kv_rank) * (T / 2) for L in m.layers)
+        res["buzopel"] = {"prefill_ms": pre, "prefill_tok_s": T / pre * 1e3, "decode_ms_per_token": dec,
+                          "decode_tok_s": 1e3 / dec, "batch_decode_ms_per_step": bdec, "batch_decode_tok_s": rows / bdec * 1e3,
+                          "active_weight_bytes_per_token": bytes_tok,
+                          "decode_frac_of_hbm": bytes_tok / (dec / 1e3) / 1e9 / hbm,
+                          "prefill_frac_of_tensor": (flops_tok + att_flops) * T / (pre / 1e3) / 1e12 / tpk,
+                          "graph_replays": eng.graph_replays, "launches": eng.launch_count}
+        del m, lm, eng, pool, caches
+        state.clear()
+        torch.cuda.empty_cache()
+        # ---- the closest existing model at equal size ---------------------------------------------------------
+        text = TextConfig(model_type="qwen2_vl", hidden_size=z["width"], num_hidden_layers=z["layers"],
+                          intermediate_size=z["top"] * z["ff"], num_attention_heads=z["heads"], rms_norm_eps=1e-6,
+                          vocab_size=z["vocab"], num_key_value_heads=max(1, z["heads"] // 4), max_position_embeddings=32768,
+                          rope_theta=1000000.0, rope_scaling={"type": "mrope", "mrope_section": [16, 24, 24]},
+                          tie_word_embeddings=False)
+        qc = QConfig(text_config=text, vision_config=VisionConfig(depth=1, embed_dim=1280, hidden_size=z["width"], num_heads=16),
+                     model_type="qwen2_vl", vocab_size=z["vocab"], eos_token_id=[])
+        qm, _ = load_synthetic("custom", seed=0, device=dev, config=qc)
+        qlm, qeng = qm.language_model, qm.engine
+
+        def q_prefill():
+            state["cache"] = make_prompt_cache(qlm)
+            emb = qm.get_input_embeddings(ids, None)
+            qlm(ids, inputs_embeds=emb.inputs_embeds, cache=state["cache"], position_ids=emb.position_ids,
+                rope_deltas=emb.rope_deltas, logits_to_keep=1, reserve_tokens=T + n_dec * (args.warmup + args.steps + 2))
+
+        def q_decode():
+            qlm.fused_greedy_decode_n(n_dec, state["cache"], reserve_tokens=T + n_dec * (args.warmup + args.steps + 2))
+
+        pre = timed(qeng, q_prefill)
+        dec = timed(qeng, q_decode) / n_dec
+        hd = z["width"] // z["heads"]
+        q_w = z["layers"] * ((z["heads"] + 2 * max(1, z["heads"] // 4)) * hd * z["width"] + z["width"] * z["width"]
+                             + 3 * z["top"] * z["ff"] * z["width"])
+        q_att = z["layers"] * 4 * z["heads"] * hd * (T / 2)
+        res["qwen2_vl_lm_equal_size"] = {
+            "prefill_ms": pre, "prefill_tok_s": T / pre * 1e3, "decode_ms_per_token": dec, "decode_tok_s": 1e3 / dec,
+            "active_weight_bytes_per_token": 2 * (q_w + head_w),
+            "decode_frac_of_hbm": 2 * (q_w + head_w) / (dec / 1e3) / 1e9 / hbm,
+            "prefill_frac_of_tensor": (2 * (q_w + head_w / T) + q_att) * T / (pre / 1e3) / 1e12 / tpk}
+        del qm, qlm, qeng
+        state.clear()
+        torch.cuda.empty_cache()
+        out["sizes"][name] = res
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -529,7 +663,24 @@ def main():
     ap.add_argument("--no-mega", action="store_true")
     ap.add_argument("--mega-mode", type=int, default=None,
                     help="decode kernel: 0 per-phase kernels, 1 k_mega (CUDA cores), 2 k_mega_tc (tcgen05)")
+    ap.add_argument("--design", default=None, choices=["buzopel"],
+                    help="instead of the default workload: prefill / decode throughput of this decoder design at "
+                         "layer sizes of real models, beside the closest existing model at equal size")
+    ap.add_argument("--design-sizes", default="", help="comma-separated subset of the sizes (default: all)")
+    ap.add_argument("--design-prompt", type=int, default=2048)
+    ap.add_argument("--design-out", type=int, default=32)
+    ap.add_argument("--design-rows", type=int, default=8)
     args = ap.parse_args()
+    if args.design:
+        import torch
+        torch.cuda.set_device(0)
+        sampler = ClockSampler(0)
+        sampler.start()
+        res = design_leg(torch.device("cuda", 0), args)
+        res.update({"design": args.design, "dtype": "bf16", "data": "synthetic (random weights, random token ids)",
+                    "steps": args.steps, "warmup": args.warmup, "clocks": sampler.stop()})
+        print(json.dumps(res))
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -400,9 +400,11 @@ int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw
                       int K, int batch, int epi, float epi_param, int round_x, int skinny, void* stream);
 /* greedy: lowest index of the largest logit per row and its log-probability */
 int b200_lm_argmax_rows(const float* z, long ldz, int V, int* tok, float* logprob, int B, void* stream);
-/* device-side token feedback of a decode loop: tok = sampled, pos += 1 for active rows; log[step][b] = sampled */
-int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* active, int* log, int log_stride, int step,
-                         int B, void* stream);
+/* device-side token feedback of a decode loop (one block): tok = sampled, pos += 1 for active rows;
+ * log[*step mod log_rows][b] = sampled (lp_log likewise = lp[b]); *step += 1 — no launch argument changes from
+ * step to step */
+int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* active, int* log, int log_stride,
+                         int log_rows, int* step, const float* lp, float* lp_log, int B, void* stream);
 
 #ifdef __cplusplus
 }

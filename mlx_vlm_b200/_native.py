@@ -122,7 +122,7 @@ LM_SIGNATURES = {
     "b200_lm_gemm_rows": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                                _I, _P]),
     "b200_lm_argmax_rows": (_I, [_P, _L, _I, _P, _P, _I, _P]),
-    "b200_lm_advance_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "b200_lm_advance_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _P]),
 }
 SIGNATURES.update(LM_SIGNATURES)
 

@@ -445,6 +445,86 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmRowsP p) {
   }
 }
 
+// The decode kernel proper: weight rows as 16-byte loads (8 bf16 per lane), the few rows of X staged in shared
+// memory chunk by chunk (rounded to bf16 there in the serving mode), every warp takes GV_R weight rows per pass.
+// Needs K % 8 == 0, 16-byte aligned weight rows and at most MR rows; the k order of a sum is fixed (lane-strided,
+// then the butterfly) whatever the other rows are.
+constexpr int GV_R = 2, GV_WARPS = 8;
+template <int MR, int GV_KC>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemm_skinny_vec_kernel(GemmRowsP p) {
+  __shared__ __align__(16) float xs[MR][GV_KC];
+  __shared__ int xrow[MR], yrow[MR];
+  const int b = blockIdx.z;
+  const int rows = min(p.count ? p.count[b] : p.M, MR);
+  if (rows <= 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x < MR) {
+    int xr = -1, yr = -1;
+    if ((int)threadIdx.x < rows) {
+      if (p.list) { const int e = p.list[(long)b * p.list_stride + threadIdx.x]; xr = e / p.x_div; yr = e; }
+      else { xr = yr = threadIdx.x; }
+    }
+    xrow[threadIdx.x] = xr; yrow[threadIdx.x] = yr;
+  }
+  const float* X = p.X + (long)b * p.xb;
+  const bf16* W = p.W + (long)b * p.wb;
+  const int n0 = (blockIdx.x * GV_WARPS + warp) * GV_R;
+  float acc[GV_R][MR];
+#pragma unroll
+  for (int r = 0; r < GV_R; ++r)
+#pragma unroll
+    for (int i = 0; i < MR; ++i) acc[r][i] = 0.f;
+  for (int k0 = 0; k0 < p.K; k0 += GV_KC) {
+    const int kc = min(GV_KC, p.K - k0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < MR * (kc >> 2); e += blockDim.x) {
+      const int i = e / (kc >> 2), k = (e % (kc >> 2)) << 2;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (xrow[i] >= 0) {
+        v = *reinterpret_cast<const float4*>(X + (long)xrow[i] * p.ldx + k0 + k);
+        if (p.round_x) { v.x = rbf(v.x); v.y = rbf(v.y); v.z = rbf(v.z); v.w = rbf(v.w); }
+      }
+      *reinterpret_cast<float4*>(&xs[i][k]) = v;
+    }
+    __syncthreads();
+    for (int k = lane * 8; k < kc; k += 256) {
+      float w[GV_R][8];
+#pragma unroll
+      for (int r = 0; r < GV_R; ++r) {
+        if (n0 + r < p.N) {
+          unpack8(ldg_stream(W + (long)(n0 + r) * p.ldw + k0 + k), w[r]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w[r][j] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < MR; ++i) {
+        const float4 a = *reinterpret_cast<const float4*>(&xs[i][k]);
+        const float4 c = *reinterpret_cast<const float4*>(&xs[i][k + 4]);
+#pragma unroll
+        for (int r = 0; r < GV_R; ++r) {
+          float t = acc[r][i];
+          t = fmaf(a.x, w[r][0], t); t = fmaf(a.y, w[r][1], t); t = fmaf(a.z, w[r][2], t); t = fmaf(a.w, w[r][3], t);
+          t = fmaf(c.x, w[r][4], t); t = fmaf(c.y, w[r][5], t); t = fmaf(c.z, w[r][6], t); t = fmaf(c.w, w[r][7], t);
+          acc[r][i] = t;
+        }
+      }
+    }
+  }
+  float* Y = p.Y + (long)b * p.yb;
+#pragma unroll
+  for (int r = 0; r < GV_R; ++r) {
+    const int n = n0 + r;
+    const float bias = (p.bias && n < p.N) ? bf2f(p.bias[n]) : 0.f;
+#pragma unroll
+    for (int i = 0; i < MR; ++i) {
+      const float v = warp_sum(acc[r][i]);
+      if (lane == 0 && n < p.N && yrow[i] >= 0) Y[(long)yrow[i] * p.ldy + n] = gemm_epi(v + bias, p.epi, p.epi_param);
+    }
+  }
+}
+
 // greedy pick per row: lowest index of the largest logit, and its log-probability
 __global__ void argmax_rows_kernel(const float* __restrict__ z, long ldz, int V, int* __restrict__ tok,
                                    float* __restrict__ logprob) {
@@ -478,14 +558,21 @@ __global__ void argmax_rows_kernel(const float* __restrict__ z, long ldz, int V,
   }
 }
 
-// decode bookkeeping on the device: the sampled tokens become the next step's inputs, positions advance
+// decode bookkeeping on the device (one block): the sampled tokens become the next step's inputs, positions
+// advance, the tokens go to row (*step mod log_rows) of the log and *step counts up — nothing of a step is a
+// launch argument, so a captured step replays unchanged
 __global__ void advance_rows_kernel(const int* __restrict__ sampled, int* __restrict__ tok, int* __restrict__ pos,
-                                    const int* __restrict__ active, int* __restrict__ log, int log_stride, int step,
-                                    int B) {
-  const int b = blockIdx.x * blockDim.x + threadIdx.x;
-  if (b >= B) return;
-  if (log) log[(long)step * log_stride + b] = sampled[b];
-  if (active == nullptr || active[b]) { tok[b] = sampled[b]; pos[b] += 1; }
+                                    const int* __restrict__ active, int* __restrict__ log, int log_stride,
+                                    int log_rows, int* __restrict__ step, const float* __restrict__ lp,
+                                    float* __restrict__ lp_log, int B) {
+  const int st = *step;
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    if (log) log[(long)(st % log_rows) * log_stride + b] = sampled[b];
+    if (lp_log) lp_log[(long)(st % log_rows) * log_stride + b] = lp[b];
+    if (active == nullptr || active[b]) { tok[b] = sampled[b]; pos[b] += 1; }
+  }
+  if (threadIdx.x == 0) *step = st + 1;
 }
 
 unsigned long long g_attn_attr_f32 = 0, g_attn_attr_bf16 = 0;
@@ -595,7 +682,17 @@ int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw
   B200_REQUIRE((list == nullptr) == (count == nullptr), "lm_gemm_rows: a row list needs its counts");
   GemmRowsP p{X, ldx, xb, (const bf16*)W, ldw, wb, (const bf16*)bias, Y, ldy, yb, list, list_stride, count,
               x_div > 0 ? x_div : 1, M, N, K, epi, epi_param, round_x};
-  if (skinny) {
+  const bool vec = K % 8 == 0 && ldw % 8 == 0 && wb % 8 == 0 && ldx % 4 == 0 && xb % 4 == 0 &&
+                   ((uintptr_t)W & 15) == 0 && ((uintptr_t)X & 15) == 0;
+  if (skinny && vec && M <= 16) {
+    dim3 grid(cdiv(N, GV_WARPS * GV_R), 1, batch);
+    const cudaStream_t cs = (cudaStream_t)st;
+    if (M <= 1) gemm_skinny_vec_kernel<1, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
+    else if (M <= 2) gemm_skinny_vec_kernel<2, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
+    else if (M <= 4) gemm_skinny_vec_kernel<4, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
+    else if (M <= 8) gemm_skinny_vec_kernel<8, 1024><<<grid, GV_WARPS * 32, 0, cs>>>(p);
+    else gemm_skinny_vec_kernel<16, 512><<<grid, GV_WARPS * 32, 0, cs>>>(p);
+  } else if (skinny) {
     dim3 grid(cdiv(N, 8), 1, batch);
     gemm_skinny_kernel<<<grid, 256, 0, (cudaStream_t)st>>>(p);
   } else {
@@ -613,10 +710,11 @@ int b200_lm_argmax_rows(const float* z, long ldz, int V, int* tok, float* logpro
   return B200_OK;
 }
 
-int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* active, int* log, int log_stride, int step,
-                         int B, void* st) {
-  B200_REQUIRE(sampled && tok && pos && B > 0, "lm_advance_rows: bad argument");
-  advance_rows_kernel<<<cdiv(B, 128), 128, 0, (cudaStream_t)st>>>(sampled, tok, pos, active, log, log_stride, step, B);
+int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* active, int* log, int log_stride,
+                         int log_rows, int* step, const float* lp, float* lp_log, int B, void* st) {
+  B200_REQUIRE(sampled && tok && pos && step && B > 0 && log_rows > 0, "lm_advance_rows: bad argument");
+  advance_rows_kernel<<<1, 128, 0, (cudaStream_t)st>>>(sampled, tok, pos, active, log, log_stride, log_rows, step, lp,
+                                                       lp_log, B);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

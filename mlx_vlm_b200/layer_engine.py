@@ -43,9 +43,16 @@ class LayerEngine:
             self._log = torch.zeros(self.TOKEN_LOG, dtype=torch.int32, device=self.device)
             self._blog = torch.zeros((self.BATCH_LOG_STEPS, self.BATCH_LOG_ROWS), dtype=torch.int32, device=self.device)
             self._blp = torch.zeros((self.BATCH_LOG_STEPS, self.BATCH_LOG_ROWS), dtype=torch.float32, device=self.device)
-            self._sampled = torch.zeros(self.BATCH_LOG_ROWS, dtype=torch.int32, device=self.device)
-            self._lp = torch.zeros(self.BATCH_LOG_ROWS, dtype=torch.float32, device=self.device)
+            self._sampled = torch.zeros(128, dtype=torch.int32, device=self.device)
+            self._lp = torch.zeros(128, dtype=torch.float32, device=self.device)
+            self._lstep = torch.zeros(1, dtype=torch.int32, device=self.device)     # device step counters of the logs
+            self._bstep_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._tok = self._pos = self._slot = self._active = None     # device state of the decode loop
+        self._states = {}
+        self._graphs = {}             # captured decode steps: (mode, rows, pool buffer, capacity) -> (graph, logits)
+        self._eager_steps = {}
+        self.use_graphs = True
+        self.graph_replays = 0
         self._logits: Optional[torch.Tensor] = None
         self._bstep = 0
 
@@ -97,12 +104,12 @@ class LayerEngine:
 
     # ------------------------------------------------------------------ one request
     def _state(self, B: int):
-        if self._tok is None or self._tok.shape[0] != B:
+        """device arrays of the decode loop, one fixed set per row count (captured steps point at them)"""
+        if B not in self._states:
             with torch.cuda.stream(self.stream):
-                self._tok = torch.zeros(B, dtype=torch.int32, device=self.device)
-                self._pos = torch.zeros(B, dtype=torch.int32, device=self.device)
-                self._slot = torch.zeros(B, dtype=torch.int32, device=self.device)
-                self._active = torch.ones(B, dtype=torch.int32, device=self.device)
+                self._states[B] = [torch.zeros(B, dtype=torch.int32, device=self.device) for _ in range(3)] + \
+                                  [torch.ones(B, dtype=torch.int32, device=self.device)]
+        self._tok, self._pos, self._slot, self._active = self._states[B]
 
     def _upload_state(self, tok, pos, slot, active=None):
         B = len(tok)
@@ -133,16 +140,53 @@ class LayerEngine:
                 for b in range(B):
                     self._log[(i + b) % self.TOKEN_LOG].copy_(self._sampled[b])
         self.tokens_launched += B
+        with torch.cuda.stream(self.stream):
+            self._lstep.fill_(self.tokens_launched)
+
+    def _decode_step(self, batch: bool):
+        """one greedy step of the armed rows: forward, pick, feed back.  Every argument is device state, so after
+        two eager steps (first-use set-up) the step is captured as a CUDA graph per (rows, pool buffer) and replayed."""
+        B = self._tok.shape[0]
+
+        def body():
+            logits = self.forward(self._tok, self._slot, self._pos)
+            self.ops.argmax_rows(logits, self._sampled[:B], self._lp[:B])
+            if batch:
+                self.ops.advance_rows(self._sampled[:B], self._tok, self._pos, self._active, self._blog, self._bstep_dev,
+                                      self._lp[:B], self._blp)
+            else:
+                self.ops.advance_rows(self._sampled[:B], self._tok, self._pos, None, self._log.view(-1, 1), self._lstep)
+            return logits
+
+        key = (batch, B, self.pool.buf.data_ptr(), self.pool.capacity)
+        if not self.use_graphs:
+            self._logits = body()
+        elif key in self._graphs:
+            g, self._logits = self._graphs[key]
+            with torch.cuda.stream(self.stream):
+                g.replay()
+            self.graph_replays += 1
+        elif self._eager_steps.get(key, 0) < 2:
+            self._eager_steps[key] = self._eager_steps.get(key, 0) + 1
+            self._logits = body()
+        else:
+            if len(self._graphs) >= 8:       # pools that moved leave stale graphs behind
+                self._graphs.clear()
+            g = torch.cuda.CUDAGraph()
+            self.stream.synchronize()
+            with torch.cuda.graph(g, stream=self.stream):
+                logits = body()
+            self._graphs[key] = (g, logits)
+            self._logits = logits
+            with torch.cuda.stream(self.stream):
+                g.replay()
+            self.graph_replays += 1
 
     def decode(self, n_steps: int):
         """n greedy steps of the armed single request; the token feedback stays on the device"""
         assert self._tok is not None and self._tok.shape[0] == 1, "decode: arm one request first (set_next / prefill)"
         for _ in range(int(n_steps)):
-            logits = self.forward(self._tok, self._slot, self._pos)
-            self._logits = logits
-            self.ops.argmax_rows(logits, self._sampled[:1], self._lp[:1])
-            i = self.tokens_launched % self.TOKEN_LOG
-            self.ops.advance_rows(self._sampled[:1], self._tok, self._pos, None, self._log[i:i + 1], 0)
+            self._decode_step(batch=False)
             self.tokens_launched += 1
 
     def fetch_tokens(self, start: int, n: int, host: torch.Tensor):
@@ -162,16 +206,15 @@ class LayerEngine:
         B = len(tok)
         assert B <= self.BATCH_LOG_ROWS
         self._upload_state(tok, pos, list(range(B)), active)
+        with torch.cuda.stream(self.stream):
+            self._bstep_dev.zero_()
         self._batch_B, self._bstep = B, 0
 
     def batch_decode(self, n_steps: int, want_logprobs: bool = False):
-        B = self._batch_B
+        assert self._tok.shape[0] == self._batch_B, "batch_decode: arm the rows first (batch_begin)"
         for _ in range(int(n_steps)):
             assert self._bstep < self.BATCH_LOG_STEPS, "batch_decode: re-arm the rows (batch_begin)"
-            logits = self.forward(self._tok, self._slot, self._pos)
-            self._logits = logits
-            self.ops.argmax_rows(logits, self._sampled[:B], self._blp[self._bstep, :B])
-            self.ops.advance_rows(self._sampled[:B], self._tok, self._pos, self._active, self._blog, self._bstep)
+            self._decode_step(batch=True)
             self._bstep += 1
 
     def batch_fetch(self, first_step: int, n_steps: int, tok_host: torch.Tensor, lp_host: Optional[torch.Tensor] = None):

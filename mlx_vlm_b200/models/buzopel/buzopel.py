@@ -92,18 +92,27 @@ class Model:
         return self
 
     def init_random(self, seed: int = 0):
-        """seeded random weights of this configuration (benchmarks, no checkpoint)"""
-        g = torch.Generator().manual_seed(seed)
-        ck = {}
-        for n in self.expected_tensors():
-            shape = self._ckpt_shape(n)
-            if len(shape) == 1:
-                mean = 1.0 if n.endswith(("dq.norm", "dkv.norm")) else 0.0
-                ck[n] = (mean + 0.05 * torch.randn(shape, generator=g)).bfloat16()
-            else:
-                s = 1.0 / self.embed_scale if n == "embed" else 1.0 / float(shape[1]) ** 0.5
-                ck[n] = (torch.randn(shape, generator=g) * s).bfloat16()
-        return self.load_weights(ck)
+        """seeded random weights of this configuration, generated on the device straight into the arena
+        (benchmarks, no checkpoint): matrices N(0, 1/fan-in), norm weights around their neutral value"""
+        eng = self._engine()
+        g = torch.Generator(device=eng.device).manual_seed(seed)
+        with torch.cuda.stream(eng.stream):
+            self.arena = WeightArena(self.manifest(), eng.device)
+            view = self.arena.view
+            for name, shape in self.manifest():
+                v = view(name)
+                if len(shape) == 1:
+                    mean = 1.0 if name.endswith(("dq.norm", "dkv.norm")) else 0.0
+                    v.copy_(mean + 0.05 * torch.randn(shape, generator=g, device=eng.device))
+                else:
+                    s = 1.0 / self.embed_scale if name == "embed" else 1.0 / float(shape[-1]) ** 0.5
+                    for part in (v.unbind(0) if v.numel() > (1 << 28) else (v,)):     # bounded fp32 staging
+                        part.copy_(torch.randn(part.shape, generator=g, device=eng.device) * s)
+            for i, L in enumerate(self.layers):
+                L.bind(f"l{i}.", view)
+            self.embed, self.final_norm, self.head = view("embed"), view("final.norm"), view("head")
+        eng.stream.synchronize()
+        return self
 
     def _ckpt_shape(self, name: str):
         W, V = self.width, self.vocab

@@ -83,6 +83,9 @@ class LatentAttention:
             view(p + n).copy_(ck[p + n])
         # the key up-projection per head, transposed: it is applied to the QUERY (absorbed form)
         view(p + "ukT").copy_(ck[p + "uk"].view(self.H, self.dim, self.kv_rank).transpose(1, 2))
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
         self.w = {n[len(p):]: view(n) for n, _ in self.manifest(p)}
 
     def forward(self, ctx: StepCtx, x: torch.Tensor) -> torch.Tensor:
@@ -126,6 +129,9 @@ class ExpertMixture:
         for e in range(self.E):
             up[e].copy_(ck[p + f"e{e}.up"])
             down[e].copy_(ck[p + f"e{e}.down"])
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
         self.w = {n[len(p):]: view(n) for n, _ in self.manifest(p)}
 
     def forward(self, ctx: StepCtx, x: torch.Tensor):
@@ -169,12 +175,19 @@ class PostNormLayer:
 
     def pack(self, p: str, ck, view):
         view(p + "norm1").copy_(ck[p + "norm1"])
-        self.w["norm1"] = view(p + "norm1")
         self.mixer.pack(p + "mix.", ck, view)
         if self.ff is not None:
             view(p + "norm2").copy_(ck[p + "norm2"])
-            self.w["norm2"] = view(p + "norm2")
             self.ff.pack(p + "mlp.", ck, view)
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        """point the blocks at their views of the arena (after packing a checkpoint or filling the arena directly)"""
+        self.w["norm1"] = view(p + "norm1")
+        self.mixer.bind(p + "mix.", view)
+        if self.ff is not None:
+            self.w["norm2"] = view(p + "norm2")
+            self.ff.bind(p + "mlp.", view)
 
     def forward(self, ctx: StepCtx, x: torch.Tensor):
         ops = ctx.ops

@@ -137,8 +137,9 @@ class LayerOps:
         self._ok(self.lib.b200_lm_argmax_rows(z.data_ptr(), z.stride(0), V, tok.data_ptr(), N.ptr(logprob), B, self.s),
                  "lm_argmax_rows")
 
-    def advance_rows(self, sampled, tok, pos, active=None, log=None, step=0):
+    def advance_rows(self, sampled, tok, pos, active, log, step, lp=None, lp_log=None):
+        """log (and lp_log): (rows, B-wide) rings, step: (1,) int32 device counter (row = step mod rows; counts up)"""
         B = tok.shape[0]
         self._ok(self.lib.b200_lm_advance_rows(sampled.data_ptr(), tok.data_ptr(), pos.data_ptr(), N.ptr(active),
-                                               N.ptr(log), log.stride(0) if log is not None else 0, int(step), B,
-                                               self.s), "lm_advance_rows")
+                                               log.data_ptr(), log.stride(0), log.shape[0], step.data_ptr(),
+                                               N.ptr(lp), N.ptr(lp_log), B, self.s), "lm_advance_rows")
