@@ -384,10 +384,11 @@ int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wk
 int b200_lm_rope_q(const float* q, long ldq, int qh_stride, int dim, float* qa, long ldqa, int Dl, int kv_rank,
                    const float* cs, int H, int rot_dim, int rot_dims, int T, void* stream);
 /* absorbed latent attention: out[t][h] = softmax_j(scale * qa[t][h] . cache[slot[t]][j]) . cache[..][j][0:kv_rank],
- * j = 0..pos[t] */
+ * j = 0..pos[t].  n_split > 1 (decode: few queries, many keys): the key tiles are dealt to n_split blocks per
+ * (token, head group), partial sums go to part [T][H][n_split][kv_rank + 2] and a second kernel merges them */
 int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int cache_bf16, long slot_stride,
                              long tok_stride, const int* slot, const int* pos, float* out, long ldo, int H, int Dl,
-                             int kv_rank, float scale, int round_q, int T, void* stream);
+                             int kv_rank, float scale, int round_q, float* part, int n_split, int T, void* stream);
 /* the `top` largest of z[t][0..E) (lowest index wins a tie) and the softmax over them */
 int b200_lm_router_topk(const float* z, long ldz, int E, int top, int* idx, float* wgt, int T, void* stream);
 /* list[e][0..count[e]) = the entries i (ascending) with idx[i] == e */
@@ -398,6 +399,19 @@ int b200_lm_moe_group(const int* idx, int n_entries, int E, int* list, long list
 int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw, long wb, const void* bias, float* Y,
                       long ldy, long yb, const int* list, long list_stride, const int* count, int x_div, int M, int N,
                       int K, int batch, int epi, float epi_param, int round_x, int skinny, void* stream);
+/* operands of the tensor-core products of a prompt step (bf16 serving mode; the products are b200_gemm_wt_f32 with
+ * one bf16 part): fp32 rows -> bf16 rows zero-padded to Kp columns (gather: src row = map[i] / div; relu2: the
+ * experts' activation before the rounding); fp32 rows scattered to dst_map[i]; the causal softmax of score rows
+ * (row r = query r / H at pos[r / H]) as bf16 probabilities; the latent columns of a slot's cache rows transposed
+ * to [kv_rank][Sp] */
+int b200_lm_rows_to_bf16(const float* X, long ldx, const int* map, int div, void* out, long ldo, int T, int K, int Kp,
+                         int relu2, void* stream);
+int b200_lm_rows_scatter(const float* X, long ldx, const int* dst_map, float* out, long ldo, int T, int K, void* stream);
+/* order[sum(count[0..e)) + i] = list[e][i]: the (token, choice) entries sorted by expert */
+int b200_lm_moe_order(const int* list, long list_stride, const int* count, int E, int* order, void* stream);
+int b200_lm_masked_softmax_bf16(const float* S, long lds, const int* pos, int H, float scale, void* P, long ldp,
+                                int rows, int Sp, void* stream);
+int b200_lm_cache_transpose(const void* cache_rows, long tok_stride, int S, int Sp, int kv_rank, void* out, void* stream);
 /* greedy: lowest index of the largest logit per row and its log-probability */
 int b200_lm_argmax_rows(const float* z, long ldz, int V, int* tok, float* logprob, int B, void* stream);
 /* device-side token feedback of a decode loop (one block): tok = sampled, pos += 1 for active rows;

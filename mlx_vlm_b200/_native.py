@@ -116,12 +116,18 @@ LM_SIGNATURES = {
     "b200_lm_norm_rows": (_I, [_P, _L, _P, _I, _P, _F, _F, _P, _L, _I, _P, _I, _I, _P]),
     "b200_lm_latent_post": (_I, [_P, _L, _P, _P, _F, _P, _L, _P, _I, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "b200_lm_rope_q": (_I, [_P, _L, _I, _I, _P, _L, _I, _I, _P, _I, _I, _I, _I, _P]),
-    "b200_lm_latent_attention": (_I, [_P, _L, _P, _I, _L, _L, _P, _P, _P, _L, _I, _I, _I, _F, _I, _I, _P]),
+    "b200_lm_latent_attention": (_I, [_P, _L, _P, _I, _L, _L, _P, _P, _P, _L, _I, _I, _I, _F, _I, _P, _I, _I, _P]),
     "b200_lm_router_topk": (_I, [_P, _L, _I, _I, _P, _P, _I, _P]),
     "b200_lm_moe_group": (_I, [_P, _I, _I, _P, _L, _P, _P]),
     "b200_lm_gemm_rows": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                                _I, _P]),
     "b200_lm_argmax_rows": (_I, [_P, _L, _I, _P, _P, _I, _P]),
+    "b200_lm_rows_to_bf16": (_I, [_P, _L, _P, _I, _P, _L, _I, _I, _I, _I, _P]),
+    "b200_lm_moe_order": (_I, [_P, _L, _P, _I, _P, _P]),
+    "b200_lm_rows_scatter": (_I, [_P, _L, _P, _P, _L, _I, _I, _P]),
+    "b200_lm_masked_softmax_bf16": (_I, [_P, _L, _P, _I, _F, _P, _L, _I, _I, _P]),
+    "b200_lm_cache_transpose": (_I, [_P, _L, _I, _I, _I, _P, _P]),
+    "b200_gemm_wt_f32": (_I, [_P, _L, _P, _L, _P, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P]),
     "b200_lm_advance_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _P]),
 }
 SIGNATURES.update(LM_SIGNATURES)

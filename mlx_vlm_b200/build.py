@@ -3,8 +3,8 @@
 `python -m mlx_vlm_b200.build [target]` or `build(target=...)`; each .so lands next to this file so
 it travels with the repo snapshot to the GPU box (it is git-ignored).  Targets:
   b200vlm   the whole C ABI (every model family)
-  b200lm    the layer-level ops alone (decoder designs assembled layer by layer on the host): a
-            fresh checkout that only serves such a model compiles two small files
+  b200lm    the layer-level ops alone (decoder designs assembled layer by layer on the host): with the
+            tcgen05 GEMM they feed: a fresh checkout that only serves such a model compiles four files
 """
 from __future__ import annotations
 
@@ -16,9 +16,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200vlm.so")
-LM_SOURCES = ["errors.cu", "layer_ops.cu"]
+LM_SOURCES = ["errors.cu", "layer_ops.cu", "gemm_wt.cu", "tower_f32.cu"]
 SOURCES = LM_SOURCES + ["engine.cu", "gemm_tcgen05.cu", "rowops.cu", "attention.cu", "decode.cu", "decode_mega.cu",
-           "decode_mega_tc.cu", "attention_tc.cu", "gemm_wt.cu", "attention_fa.cu", "decode_batch.cu", "tower_f32.cu"]
+           "decode_mega_tc.cu", "attention_tc.cu", "attention_fa.cu", "decode_batch.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -181,7 +181,9 @@ struct LatAttnP {
   int H, Dl, kv_rank;
   float scale;
   int round_q;                           // bf16 serving mode: the query operand is rounded like the keys
-};
+  float* part;                           // n_split > 1: [T][H][n_split][kv_rank + 2] = (acc.., max, sum) per split
+  int n_split;                           // key tiles are dealt round-robin to gridDim.z splits (decode: few queries,
+};                                       // many keys), a second kernel merges the splits
 template <typename CT>
 __global__ void latent_attention_kernel(LatAttnP<CT> p) {
   extern __shared__ float sm[];
@@ -202,7 +204,7 @@ __global__ void latent_attention_kernel(LatAttnP<CT> p) {
   float acc[32];                          // kv_rank <= 1024
 #pragma unroll
   for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-  for (int k0 = 0; k0 < n_keys; k0 += LA_KT) {
+  for (int k0 = blockIdx.z * LA_KT; k0 < n_keys; k0 += LA_KT * p.n_split) {
     const int nk = min(LA_KT, n_keys - k0);
     __syncthreads();
     for (int e = threadIdx.x; e < nk * Dl; e += blockDim.x) {
@@ -239,6 +241,17 @@ __global__ void latent_attention_kernel(LatAttnP<CT> p) {
     }
   }
   if (!live) return;
+  if (p.n_split > 1) {                    // un-normalised partial sums; a split without keys has max -inf, sum 0
+    float* o = p.part + (((long)t * p.H + h) * p.n_split + blockIdx.z) * (p.kv_rank + 2);
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < per_lane) {
+        const int d = lane + 32 * i;
+        if (d < p.kv_rank) o[d] = acc[i];
+      }
+    if (lane == 0) { o[p.kv_rank] = m; o[p.kv_rank + 1] = l; }
+    return;
+  }
   const float inv = 1.0f / l;
   float* o = p.out + (long)t * p.ldo + (long)h * p.kv_rank;
 #pragma unroll
@@ -247,6 +260,29 @@ __global__ void latent_attention_kernel(LatAttnP<CT> p) {
       const int d = lane + 32 * i;
       if (d < p.kv_rank) o[d] = acc[i] * inv;
     }
+}
+
+// merge the splits of one (token, head) in a fixed order: out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M)
+__global__ void latent_attention_merge_kernel(const float* __restrict__ part, int n_split, int kv_rank,
+                                              float* __restrict__ out, long ldo, int H) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* pp = part + ((long)t * H + h) * n_split * (kv_rank + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < n_split; ++s) M = fmaxf(M, pp[(long)s * (kv_rank + 2) + kv_rank]);
+  float L = 0.f;
+  for (int s = 0; s < n_split; ++s) {
+    const float* q = pp + (long)s * (kv_rank + 2);
+    L += q[kv_rank + 1] * expf(q[kv_rank] - M);
+  }
+  const float inv = 1.0f / L;
+  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+      const float* q = pp + (long)s * (kv_rank + 2);
+      a += q[d] * expf(q[kv_rank] - M);
+    }
+    out[(long)t * ldo + (long)h * kv_rank + d] = a * inv;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -525,6 +561,74 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemm_skinny_vec_kernel(GemmRows
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Operands of the tensor-core products of a prompt step (bf16 serving mode; the products themselves are the
+// weight-major tcgen05 GEMM with fp32 output, b200_gemm_wt_f32):
+// rows of fp32 numbers -> bf16 rows padded with zeros to Kp columns; optional gather (src row = map[i] / div),
+// optional relu^2 before the rounding; with `dst_map` the kernel instead scatters fp32 rows (dst row = dst_map[i])
+__global__ void rows_to_bf16_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ map, int div,
+                                    bf16* __restrict__ out, long ldo, int K, int Kp, int relu2) {
+  const int i = blockIdx.x;
+  const float* x = X + (long)(map ? map[i] / div : i) * ldx;
+  for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
+    float v = k < K ? x[k] : 0.f;
+    if (relu2) { v = fmaxf(v, 0.f); v *= v; }
+    out[(long)i * ldo + k] = f2bf(v);
+  }
+}
+__global__ void rows_scatter_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ dst_map,
+                                    float* __restrict__ out, long ldo, int K) {
+  const int i = blockIdx.x;
+  const float* x = X + (long)i * ldx;
+  float* o = out + (long)dst_map[i] * ldo;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) o[k] = x[k];
+}
+// entries sorted by expert: order[prefix[e] + i] = list[e][i], prefix = running sum of the counts
+__global__ void moe_order_kernel(const int* __restrict__ list, long list_stride, const int* __restrict__ count,
+                                 int* __restrict__ order) {
+  const int e = blockIdx.x;
+  int base = 0;
+  for (int i = 0; i < e; ++i) base += count[i];
+  const int n = count[e];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) order[base + i] = list[(long)e * list_stride + i];
+}
+// causal softmax of score rows: row r belongs to query r / H at position pos[r / H], which sees keys 0..pos;
+// P (bf16, normalised in fp32 before the rounding) is zero past the last visible key and in the padding
+__global__ void masked_softmax_bf16_kernel(const float* __restrict__ S, long lds, const int* __restrict__ pos, int H,
+                                           float scale, bf16* __restrict__ P, long ldp, int Sp) {
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  const int n = pos[r / H] + 1;
+  const float* s = S + r * lds;
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) m = fmaxf(m, s[j]);
+  m = warp_max(m);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, red[i]);
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) sum += expf((s[j] - m) * scale);
+  const float inv = 1.0f / block_sum(sum, red);
+  for (int j = threadIdx.x; j < Sp; j += blockDim.x)
+    P[r * ldp + j] = f2bf(j < n ? expf((s[j] - m) * scale) * inv : 0.f);
+}
+// the latent columns of one slot's cache rows, transposed: out[d][j] = cache[j][d] (bf16), j < S, zero up to Sp
+__global__ void cache_transpose_kernel(const bf16* __restrict__ C, long tok_stride, int S, int Sp, int kv_rank,
+                                       bf16* __restrict__ out) {
+  __shared__ bf16 tile[32][33];
+  const int j0 = blockIdx.x * 32, d0 = blockIdx.y * 32, tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int y = ty; y < 32; y += 8) {
+    const int j = j0 + y, d = d0 + tx;
+    tile[y][tx] = (j < S && d < kv_rank) ? C[(long)j * tok_stride + d] : f2bf(0.f);
+  }
+  __syncthreads();
+  for (int y = ty; y < 32; y += 8) {
+    const int d = d0 + y, j = j0 + tx;
+    if (d < kv_rank && j < Sp) out[(long)d * Sp + j] = tile[tx][y];
+  }
+}
+
 // greedy pick per row: lowest index of the largest logit, and its log-probability
 __global__ void argmax_rows_kernel(const float* __restrict__ z, long ldz, int V, int* __restrict__ tok,
                                    float* __restrict__ logprob) {
@@ -639,25 +743,30 @@ int b200_lm_rope_q(const float* q, long ldq, int qh_stride, int dim, float* qa, 
 
 int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int cache_bf16, long slot_stride,
                              long tok_stride, const int* slot, const int* pos, float* out, long ldo, int H, int Dl,
-                             int kv_rank, float scale, int round_q, int T, void* st) {
+                             int kv_rank, float scale, int round_q, float* part, int n_split, int T, void* st) {
   B200_REQUIRE(qa && cache && slot && pos && out && T > 0 && H > 0, "lm_latent_attention: bad argument");
+  if (n_split < 1 || !part) n_split = 1;
   B200_REQUIRE(kv_rank <= 1024 && kv_rank <= Dl, "lm_latent_attention: latent rank %d not supported", kv_rank);
   const int nw = H < 8 ? H : 8;
   const size_t smem = ((size_t)LA_KT * (Dl + 1) + (size_t)nw * Dl) * sizeof(float);
   B200_REQUIRE(smem <= 200 * 1024, "lm_latent_attention: rows of %d numbers do not fit shared memory", Dl);
-  dim3 grid(T, cdiv(H, nw));
+  dim3 grid(T, cdiv(H, nw), n_split);
   if (cache_bf16) {
     if (first_use_on_device(&g_attn_attr_bf16))
       B200_CUDA(cudaFuncSetAttribute(latent_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    LatAttnP<bf16> p{qa, ldqa, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q};
+    LatAttnP<bf16> p{qa, ldqa, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split};
     latent_attention_kernel<bf16><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   } else {
     if (first_use_on_device(&g_attn_attr_f32))
       B200_CUDA(cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    LatAttnP<float> p{qa, ldqa, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q};
+    LatAttnP<float> p{qa, ldqa, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split};
     latent_attention_kernel<float><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   }
   B200_CHECK_LAUNCH();
+  if (n_split > 1) {
+    latent_attention_merge_kernel<<<dim3(T, H), 128, 0, (cudaStream_t)st>>>(part, n_split, kv_rank, out, ldo, H);
+    B200_CHECK_LAUNCH();
+  }
   return B200_OK;
 }
 
@@ -699,6 +808,44 @@ int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw
     dim3 grid(cdiv(N, GB_N), cdiv(M, GB_M), batch);
     gemm_rows_kernel<<<grid, 256, 0, (cudaStream_t)st>>>(p);
   }
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_rows_to_bf16(const float* X, long ldx, const int* map, int div, void* out, long ldo, int T, int K, int Kp,
+                         int relu2, void* st) {
+  B200_REQUIRE(X && out && T > 0 && K > 0 && Kp >= K, "lm_rows_to_bf16: bad argument");
+  rows_to_bf16_kernel<<<T, 256, 0, (cudaStream_t)st>>>(X, ldx, map, div > 0 ? div : 1, (bf16*)out, ldo, K, Kp, relu2);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_rows_scatter(const float* X, long ldx, const int* dst_map, float* out, long ldo, int T, int K, void* st) {
+  B200_REQUIRE(X && dst_map && out && T > 0 && K > 0, "lm_rows_scatter: bad argument");
+  rows_scatter_kernel<<<T, 256, 0, (cudaStream_t)st>>>(X, ldx, dst_map, out, ldo, K);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_moe_order(const int* list, long list_stride, const int* count, int E, int* order, void* st) {
+  B200_REQUIRE(list && count && order && E > 0, "lm_moe_order: bad argument");
+  moe_order_kernel<<<E, 256, 0, (cudaStream_t)st>>>(list, list_stride, count, order);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_masked_softmax_bf16(const float* S, long lds, const int* pos, int H, float scale, void* P, long ldp,
+                                int rows, int Sp, void* st) {
+  B200_REQUIRE(S && pos && P && rows > 0 && H > 0 && Sp > 0, "lm_masked_softmax_bf16: bad argument");
+  masked_softmax_bf16_kernel<<<rows, 256, 0, (cudaStream_t)st>>>(S, lds, pos, H, scale, (bf16*)P, ldp, Sp);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_cache_transpose(const void* cache_rows, long tok_stride, int S, int Sp, int kv_rank, void* out, void* st) {
+  B200_REQUIRE(cache_rows && out && S > 0 && Sp >= S && kv_rank > 0, "lm_cache_transpose: bad argument");
+  cache_transpose_kernel<<<dim3(cdiv(Sp, 32), cdiv(kv_rank, 32)), 256, 0, (cudaStream_t)st>>>(
+      (const bf16*)cache_rows, tok_stride, S, Sp, kv_rank, (bf16*)out);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -84,11 +84,11 @@ class LayerEngine:
 
     # ------------------------------------------------------------------ the step
     def forward(self, tokens: torch.Tensor, slot: torch.Tensor, pos: torch.Tensor, want: Optional[torch.Tensor] = None,
-                embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
+                embeds: Optional[torch.Tensor] = None, segments=None) -> torch.Tensor:
         """tokens / slot / pos: (T,) int32 device.  want: (n,) int32 device rows whose logits are wanted (None:
         every row).  Returns fp32 logits (n, vocab).  The cache rows of the tokens are written on the way."""
         c, ops = self.core, self.ops
-        ctx = StepCtx(ops, slot, pos, self.pool, c.eps)
+        ctx = StepCtx(ops, slot, pos, self.pool, c.eps, segments)    # segments: the host's view of a prompt step
         if embeds is not None:
             with torch.cuda.stream(self.stream):
                 x = embeds.to(torch.float32).reshape(-1, c.width).clone()

@@ -76,8 +76,9 @@ class LanguageModel:
         self._bind(caches, max([o + n for o, n in zip(offs, lens)] + [reserve_tokens]))
         T = sum(lens)
         meta = np.empty((3, T), dtype=np.int32)
-        rows, at = [], 0
+        rows, at, segments = [], 0, []
         for g, (toks, c, n, o) in enumerate(zip(token_lists, caches, lens, offs)):
+            segments.append((at, n, int(c[0]._row), o))
             meta[0, at:at + n] = np.asarray(toks, dtype=np.int32)
             meta[1, at:at + n] = c[0]._row
             meta[2, at:at + n] = np.arange(o, o + n, dtype=np.int32)
@@ -91,7 +92,7 @@ class LanguageModel:
         want_dev = None if all_rows else (eng.ops.to_device(np.asarray(rows, dtype=np.int32)) if rows else None)
         if not rows:   # nothing wanted: the cache is still filled
             want_dev = eng.ops.to_device(np.asarray([T - 1], dtype=np.int32))
-        logits = eng.forward(dev[0], dev[1], dev[2], want_dev, embeds=embeds)
+        logits = eng.forward(dev[0], dev[1], dev[2], want_dev, embeds=embeds, segments=segments)
         for c, n in zip(caches, lens):
             for layer_cache in c:
                 layer_cache.offset += n

@@ -27,6 +27,7 @@ class StepCtx:
     pos: torch.Tensor             # (T,) int32 device: position of every token in its sequence
     pool: object                  # LatentPool
     eps: float
+    segments: Optional[List] = None   # host view of the step: (first token, tokens, slot, first position) per request
     _rope: Dict = field(default_factory=dict)
 
     def rope(self, base: float, dims: int) -> torch.Tensor:
@@ -103,10 +104,38 @@ class LatentAttention:
         ops.gemm(q, w["ukT"], qa, M=T, N_=r, K=dn, xb=dn + dr, ldw=dn, wb=r * dn, yb=Dl, batch=H)
         ops.rope_q(q, qa, cs, H, dn, dr, self.rot_dims, r)
         ol = ops.empty((T, H * r))
-        ops.latent_attention(qa, cache_layer, ctx.slot, ctx.pos, ol, H, r, self.scale)
+        segs = ctx.segments or []
+        if any(ops.tc_ok(n, Dl, r, cache_layer.stride(1)) for _, n, _, _ in segs) and cache_layer.dtype == torch.bfloat16:
+            for start, n, slot, p0 in segs:          # long portions on the tensor cores, the rest on the row kernel
+                sl = slice(start, start + n)
+                if ops.tc_ok(n, Dl, r, cache_layer.stride(1)):
+                    self._attend_prompt(ops, qa[sl], cache_layer[slot], ctx.pos[sl], ol[sl], p0 + n)
+                else:
+                    ops.latent_attention(qa[sl], cache_layer, ctx.slot[sl], ctx.pos[sl], ol[sl], H, r, self.scale)
+        else:
+            ops.latent_attention(qa, cache_layer, ctx.slot, ctx.pos, ol, H, r, self.scale)
         att = ops.empty((T, H * dv))
         ops.gemm(ol, w["uv"], att, M=T, N_=dv, K=r, xb=r, ldw=r, wb=dv * r, yb=dv, batch=H)
         return ops.linear(att, w["o"])
+
+
+    def _attend_prompt(self, ops: LayerOps, qa, rows, pos, ol, S: int):
+        """A portion of a prompt against the S cached rows of its slot as two tcgen05 products: the cache rows are
+        the weight-major operand of the scores (absorbed queries x rows), the causal softmax runs in fp32 over the
+        score rows, and the transposed latent columns are the operand of the weighted sum.  Queries are taken in
+        chunks that bound the score buffer."""
+        H, r, Dl = self.H, self.kv_rank, self.kv_rank + self.rot_dim
+        n, Sp = qa.shape[0], (S + 63) // 64 * 64
+        ct = ops.cache_transpose(rows, S, Sp, r)
+        step = max(1, min(n, (1 << 27) // (H * Sp)))
+        for a in range(0, n, step):
+            m = min(step, n - a)
+            qb = ops.to_bf16(qa[a:a + m].view(m * H, Dl), Dl)
+            sc = ops.empty((m * H, S))
+            ops.tc_gemm(qb, rows, sc, N_=S, K=Dl, ldw=rows.stride(0))
+            P = ops.empty((m * H, Sp), torch.bfloat16)
+            ops.masked_softmax_bf16(sc, pos[a:a + m], H, self.scale, P)
+            ops.tc_gemm(P, ct, ol[a:a + m].view(m * H, r), N_=r, K=Sp)
 
 
 class ExpertMixture:
@@ -140,6 +169,8 @@ class ExpertMixture:
         z = ops.linear(x, w["router"], bias=w["router.b"])
         idx, wgt = ops.router_topk(z, self.top)
         lists, count = ops.moe_group(idx, self.E)
+        if ops.tc_ok(T, self.W, self.ff):
+            return self._experts_prompt(ops, x, lists, count), wgt
         hid = ops.empty((T * self.top, self.ff))
         ops.gemm(x, w["up"], hid, M=T, N_=self.ff, K=self.W, wb=self.ff * self.W, batch=self.E, lists=lists,
                  count=count, x_div=self.top, epi=EPI_RELU2)
@@ -147,6 +178,35 @@ class ExpertMixture:
         ops.gemm(hid, w["down"], out, M=T, N_=self.W, K=self.ff, wb=self.W * self.ff, batch=self.E, lists=lists,
                  count=count, x_div=1)
         return out, wgt
+
+
+    def _experts_prompt(self, ops: LayerOps, x, lists, count):
+        """A prompt step on the tensor cores.  The (token, choice) entries are sorted by expert; ONE launch gathers
+        and rounds all input rows in that order, every expert with tokens runs two tcgen05 products over its
+        contiguous segment (the host reads the experts' token counts: one small copy per layer), ONE launch applies
+        relu^2 and rounds the hidden rows, ONE launch scatters the outputs back to entry order."""
+        w, T = self.w, x.shape[0]
+        n_all = T * self.top
+        order = ops.moe_order(lists, count)
+        with torch.cuda.stream(ops.stream):
+            counts = count.to("cpu").tolist()
+        xs = ops.to_bf16(x, self.W, rows=n_all, row_map=order, div=self.top)
+        hs = ops.empty((n_all, self.ff))
+        at = 0
+        for e, n in enumerate(counts):
+            if n:
+                ops.tc_gemm(xs[at:at + n], w["up"][e], hs[at:at + n], N_=self.ff, K=self.W)
+            at += n
+        hb = ops.to_bf16(hs, self.ff, relu2=True)
+        ys = ops.empty((n_all, self.W))
+        at = 0
+        for e, n in enumerate(counts):
+            if n:
+                ops.tc_gemm(hb[at:at + n], w["down"][e], ys[at:at + n], N_=self.W, K=self.ff)
+            at += n
+        out = ops.empty((n_all, self.W))
+        ops.rows_scatter(ys, order, out, n_all)
+        return out
 
 
 MIXERS = {"latent_attention": LatentAttention}

@@ -16,6 +16,9 @@ import torch
 from .. import _native as N
 
 EPI_NONE, EPI_RELU2, EPI_SOFTCAP = 0, 1, 2
+SM_COUNT = 148
+TC_MIN_ROWS = 128     # from this many rows on, a product of the bf16 serving mode runs on the tcgen05 GEMM
+WT_F32 = 3            # gemm_wt output mode: fp32 rows
 SKINNY_ROWS = 16      # up to this many rows a product runs on the warp-per-weight-row kernel
 
 
@@ -96,12 +99,18 @@ class LayerOps:
                                          kv_rank + rot_dim, kv_rank, cs.data_ptr(), H, rot_dim, rot_dims, T, self.s),
                  "lm_rope_q")
 
-    def latent_attention(self, qa, cache_layer, slot, pos, out, H, kv_rank, scale):
+    def latent_attention(self, qa, cache_layer, slot, pos, out, H, kv_rank, scale, n_split=None):
+        """n_split: blocks per (token, head group) that share the keys (None: enough to fill the GPU when the
+        step has few tokens — a decode step —, 1 for prompts)"""
         T, Dl = qa.shape[0], cache_layer.shape[-1]
+        if n_split is None:
+            groups = T * ((H + 7) // 8)
+            n_split = max(1, min(64, (2 * SM_COUNT) // groups))
+        part = self.empty((T, H, n_split, kv_rank + 2)) if n_split > 1 else None
         self._ok(self.lib.b200_lm_latent_attention(
             qa.data_ptr(), qa.stride(0), cache_layer.data_ptr(), int(cache_layer.dtype == torch.bfloat16),
             cache_layer.stride(0), cache_layer.stride(1), slot.data_ptr(), pos.data_ptr(), out.data_ptr(),
-            out.stride(0), H, Dl, kv_rank, float(scale), 0, T, self.s), "lm_latent_attention")
+            out.stride(0), H, Dl, kv_rank, float(scale), 0, N.ptr(part), n_split, T, self.s), "lm_latent_attention")
 
     def router_topk(self, z, top):
         T, E = z.shape
@@ -126,10 +135,59 @@ class LayerOps:
             lists.stride(0) if lists is not None else 0, N.ptr(count), x_div, M, N_, K, batch, epi, float(epi_param),
             int(not self.exact), int(M <= SKINNY_ROWS), self.s), "lm_gemm_rows")
 
+    # ---- the tensor-core path of prompt steps (bf16 serving mode) ----------------------------------------
+    def tc_ok(self, rows: int, *ks: int) -> bool:
+        """a product with `rows` rows and inner sizes `ks` may run on the tcgen05 GEMM: serving mode, enough rows
+        to fill a tile, 16-byte rows for the TMA"""
+        return (not self.exact) and rows >= TC_MIN_ROWS and all(k % 8 == 0 for k in ks)
+
+    def to_bf16(self, X: torch.Tensor, K: int, rows: Optional[int] = None, row_map: Optional[torch.Tensor] = None,
+                div: int = 1, relu2: bool = False) -> torch.Tensor:
+        """fp32 rows -> bf16 rows zero-padded to a multiple of 64 columns (the GEMM's k-block)"""
+        rows = X.shape[0] if rows is None else rows
+        Kp = (K + 63) // 64 * 64
+        out = self.empty((rows, Kp), torch.bfloat16)
+        self._ok(self.lib.b200_lm_rows_to_bf16(X.data_ptr(), X.stride(0), N.ptr(row_map), div, out.data_ptr(), Kp, rows,
+                                               K, Kp, int(relu2), self.s), "lm_rows_to_bf16")
+        return out
+
+    def tc_gemm(self, Xb: torch.Tensor, W: torch.Tensor, Y: torch.Tensor, *, N_: int, K: int, ldw: Optional[int] = None,
+                ldy: Optional[int] = None, bias=None, rows: Optional[int] = None):
+        """Y[rows, N_] (fp32) = Xb[rows, ceil64(K)] (bf16) . W[N_, K]^T (bf16, row pitch ldw) on tcgen05"""
+        rows = Xb.shape[0] if rows is None else rows
+        self._ok(self.lib.b200_gemm_wt_f32(Xb.data_ptr(), Xb.stride(0), W.data_ptr(), K if ldw is None else ldw,
+                                           N.ptr(bias), 0, 0, Y.data_ptr(), Y.stride(0) if ldy is None else ldy, 0, 0, 0,
+                                           rows, N_, K, 1, 0, WT_F32, self.s), "gemm_wt_f32")
+
+    def moe_order(self, lists: torch.Tensor, count: torch.Tensor) -> torch.Tensor:
+        E, T = lists.shape
+        order = self.empty((lists.numel(),), torch.int32)      # T * top entries at most (each entry is in one list)
+        self._ok(self.lib.b200_lm_moe_order(lists.data_ptr(), lists.stride(0), count.data_ptr(), E, order.data_ptr(),
+                                            self.s), "lm_moe_order")
+        return order
+
+    def rows_scatter(self, X: torch.Tensor, dst_map: torch.Tensor, out: torch.Tensor, rows: int):
+        self._ok(self.lib.b200_lm_rows_scatter(X.data_ptr(), X.stride(0), dst_map.data_ptr(), out.data_ptr(),
+                                               out.stride(0), rows, X.shape[1], self.s), "lm_rows_scatter")
+
+    def masked_softmax_bf16(self, S: torch.Tensor, pos: torch.Tensor, H: int, scale: float, P: torch.Tensor):
+        self._ok(self.lib.b200_lm_masked_softmax_bf16(S.data_ptr(), S.stride(0), pos.data_ptr(), H, float(scale),
+                                                      P.data_ptr(), P.stride(0), S.shape[0], P.shape[1], self.s),
+                 "lm_masked_softmax_bf16")
+
+    def cache_transpose(self, rows: torch.Tensor, S: int, Sp: int, kv_rank: int) -> torch.Tensor:
+        out = self.empty((kv_rank, Sp), torch.bfloat16)
+        self._ok(self.lib.b200_lm_cache_transpose(rows.data_ptr(), rows.stride(0), S, Sp, kv_rank, out.data_ptr(), self.s),
+                 "lm_cache_transpose")
+        return out
+
     def linear(self, X: torch.Tensor, W: torch.Tensor, bias=None, epi=EPI_NONE, epi_param=0.0) -> torch.Tensor:
         (T, K), n = X.shape, W.shape[0]
         Y = self.empty((T, n))
-        self.gemm(X, W, Y, M=T, N_=n, K=K, bias=bias, epi=epi, epi_param=epi_param)
+        if epi == EPI_NONE and self.tc_ok(T, K):
+            self.tc_gemm(self.to_bf16(X, K), W, Y, N_=n, K=K, bias=bias)
+        else:
+            self.gemm(X, W, Y, M=T, N_=n, K=K, bias=bias, epi=epi, epi_param=epi_param)
         return Y
 
     def argmax_rows(self, z, tok, logprob=None):

@@ -329,6 +329,27 @@ def test_slots_released_and_used_again_and_more_slots():
     assert rel(got, O.forward(cfg, W, c + [5])[-1:]) < TOL["float32"]
 
 
+def test_long_prompt_paths_of_the_serving_mode():
+    """prompts of 128 tokens and more take the tensor-core products (projections, attention against the cached
+    rows, experts over sorted segments): a long portion after a cached prefix, experts that get one or two tokens
+    or none, sizes that are multiples of 8 but not of 64, a batch whose short member stays on the row kernels"""
+    cfg = config([layer(heads=3, dim=24, rot=8, vdim=16, kv_rank=40, q_rank=56, experts=48, top=1, ff=40),
+                  layer(heads=3, dim=24, rot=8, vdim=16, kv_rank=40, q_rank=56, experts=3, top=2, ff=24, kv_from=0)],
+                 width=72, vocab=90)
+    model, W = build(cfg, "bfloat16", seed=4)
+    exact, _ = build(cfg, "float32", seed=4)
+    lm, eng = model.language_model, model.engine
+    toks = tokens(330, cfg["vocab"], 9)
+    ref = O.forward(cfg, W, toks)
+    got = run_alone(model, toks, [140, 150, 40])
+    assert rel(got, ref, "bfloat16") < TOL["bfloat16"]
+    assert rel(run_alone(exact, toks, [140, 150, 40]), ref) < TOL["float32"]
+    pool = lm.make_pool(2, 512)
+    ca, cb = lm.make_cache_row(pool, 0), lm.make_cache_row(pool, 1)
+    both = host(eng, lm.step([toks[:200], toks[:30]], [ca, cb], want=[list(range(200)), list(range(30))]))
+    assert rel(both[:200], ref[:200], "bfloat16") < TOL["bfloat16"] and rel(both[200:], ref[:30], "bfloat16") < TOL["bfloat16"]
+
+
 def test_long_decoding():
     cfg = config(layers=[layer(), layer(kv_from=0)])
     model, W = build(cfg)
