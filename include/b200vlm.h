@@ -320,6 +320,12 @@ int b200_f32_gather_rows(const float* in, long ld_in, const int* idx, int n_idx,
 int b200_gemm_wt_f32(const void* X, long ldx, const void* W, long ldw, const void* bias, const float* res32,
                      long ldr32, float* C32, long ldc32, void* Csplit, long ld_split, int n_pad, int T, int N,
                      int K_w, int n_parts, int epilogue, int mode, void* stream);
+/* many independent small Linears of one shape family in one call (a mixture's experts over their token segments, the
+ * heads of a per-head projection): product i is C32 + c_off[i] [rows[i], N] = (X + x_off[i]) . (W + w_off[i])^T, one
+ * bf16 part, offsets in elements, launched round-robin on `streams` (ordered by the caller's events) */
+int b200_gemm_wt_f32_many(const void* X, long ldx, const void* W, long ldw, float* C32, long ldc32, const long* x_off,
+                          const long* w_off, const long* c_off, const int* rows, int n, int N, int K_w,
+                          void* const* streams, int n_streams);
 
 /* ------------------------------------------------------------------------- */
 /* Lock-step batched decode (continuous batching; generate/ar.py:929-1390        */

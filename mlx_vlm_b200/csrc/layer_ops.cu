@@ -183,7 +183,9 @@ struct LatAttnP {
   int round_q;                           // bf16 serving mode: the query operand is rounded like the keys
   float* part;                           // n_split > 1: [T][H][n_split][kv_rank + 2] = (acc.., max, sum) per split
   int n_split;                           // key tiles are dealt round-robin to gridDim.z splits (decode: few queries,
-};                                       // many keys), a second kernel merges the splits
+                                         // many keys), a second kernel merges the splits
+  int vec8;                              // bf16 cache rows start on 16-byte boundaries and Dl % 8 == 0
+};
 template <typename CT>
 __global__ void latent_attention_kernel(LatAttnP<CT> p) {
   extern __shared__ float sm[];
@@ -207,9 +209,20 @@ __global__ void latent_attention_kernel(LatAttnP<CT> p) {
   for (int k0 = blockIdx.z * LA_KT; k0 < n_keys; k0 += LA_KT * p.n_split) {
     const int nk = min(LA_KT, n_keys - k0);
     __syncthreads();
-    for (int e = threadIdx.x; e < nk * Dl; e += blockDim.x) {
-      const int j = e / Dl, i = e % Dl;
-      keys[j * ldk + i] = ld_act(base + (long)(k0 + j) * p.tok_stride + i);
+    if (sizeof(CT) == 2 && p.vec8) {         // bf16 rows as 16-byte loads
+      const int per_row = Dl >> 3;
+      for (int e = threadIdx.x; e < nk * per_row; e += blockDim.x) {
+        const int j = e / per_row, i = (e - j * per_row) << 3;
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(base + (long)(k0 + j) * p.tok_stride + i), f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) keys[j * ldk + i + u] = f[u];
+      }
+    } else {
+      for (int e = threadIdx.x; e < nk * Dl; e += blockDim.x) {
+        const int j = e / Dl, i = e % Dl;
+        keys[j * ldk + i] = ld_act(base + (long)(k0 + j) * p.tok_stride + i);
+      }
     }
     __syncthreads();
     if (!live) continue;
@@ -265,22 +278,29 @@ __global__ void latent_attention_kernel(LatAttnP<CT> p) {
 // merge the splits of one (token, head) in a fixed order: out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M)
 __global__ void latent_attention_merge_kernel(const float* __restrict__ part, int n_split, int kv_rank,
                                               float* __restrict__ out, long ldo, int H) {
-  const int t = blockIdx.x, h = blockIdx.y;
-  const float* pp = part + ((long)t * H + h) * n_split * (kv_rank + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < n_split; ++s) M = fmaxf(M, pp[(long)s * (kv_rank + 2) + kv_rank]);
-  float L = 0.f;
-  for (int s = 0; s < n_split; ++s) {
-    const float* q = pp + (long)s * (kv_rank + 2);
-    L += q[kv_rank + 1] * expf(q[kv_rank] - M);
+  __shared__ float wgt[64];
+  __shared__ float inv_s;
+  const int t = blockIdx.x, h = blockIdx.y, row = kv_rank + 2;
+  const float* pp = part + ((long)t * H + h) * n_split * row;
+  if (threadIdx.x < 32) {                  // n_split <= 64: two per lane
+    const int s0 = threadIdx.x, s1 = threadIdx.x + 32;
+    const float m0 = s0 < n_split ? pp[(long)s0 * row + kv_rank] : -INFINITY;
+    const float m1 = s1 < n_split ? pp[(long)s1 * row + kv_rank] : -INFINITY;
+    const float l0 = s0 < n_split ? pp[(long)s0 * row + kv_rank + 1] : 0.f;
+    const float l1 = s1 < n_split ? pp[(long)s1 * row + kv_rank + 1] : 0.f;
+    const float M = warp_max(fmaxf(m0, m1));
+    const float e0 = expf(m0 - M), e1 = expf(m1 - M);
+    wgt[s0] = e0; wgt[s1] = e1;
+    // fixed order: lane-local pair, then the butterfly
+    const float L = warp_sum(l0 * e0 + l1 * e1);
+    if (threadIdx.x == 0) inv_s = 1.0f / L;
   }
-  const float inv = 1.0f / L;
+  __syncthreads();
+  const float inv = inv_s;
   for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
     float a = 0.f;
-    for (int s = 0; s < n_split; ++s) {
-      const float* q = pp + (long)s * (kv_rank + 2);
-      a += q[d] * expf(q[kv_rank] - M);
-    }
+#pragma unroll 8
+    for (int s = 0; s < n_split; ++s) a = fmaf(pp[(long)s * row + d], wgt[s], a);
     out[(long)t * ldo + (long)h * kv_rank + d] = a * inv;
   }
 }
@@ -523,6 +543,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemm_skinny_vec_kernel(GemmRows
       *reinterpret_cast<float4*>(&xs[i][k]) = v;
     }
     __syncthreads();
+#pragma unroll 4
     for (int k = lane * 8; k < kc; k += 256) {
       float w[GV_R][8];
 #pragma unroll
@@ -707,7 +728,7 @@ int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const
   B200_REQUIRE(y && w && x && T > 0 && N > 0, "lm_norm_rows: bad argument");
   B200_REQUIRE((N + 32) * 4 <= 48 * 1024, "lm_norm_rows: rows of %d numbers do not fit shared memory", N);
   NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, x, ldx, add, rows, N};
-  norm_rows_kernel<<<T, 256, (N + 32) * sizeof(float), (cudaStream_t)st>>>(p);
+  norm_rows_kernel<<<T, T < 64 ? 1024 : 256, (N + 32) * sizeof(float), (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
@@ -722,11 +743,11 @@ int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wk
   if (cache_bf16) {
     LatentPostP<bf16> p{D, ldd, (const bf16*)wq, (const bf16*)wkv, eps, cq, ldq, (bf16*)cache, slot_stride, tok_stride,
                         slot, pos, (const float2*)cs, q_rank, kv_rank, rot_dim, rot_dims, own_kv};
-    latent_post_kernel<bf16><<<T, 128, 0, (cudaStream_t)st>>>(p);
+    latent_post_kernel<bf16><<<T, T < 64 ? 512 : 128, 0, (cudaStream_t)st>>>(p);
   } else {
     LatentPostP<float> p{D, ldd, (const bf16*)wq, (const bf16*)wkv, eps, cq, ldq, (float*)cache, slot_stride,
                          tok_stride, slot, pos, (const float2*)cs, q_rank, kv_rank, rot_dim, rot_dims, own_kv};
-    latent_post_kernel<float><<<T, 128, 0, (cudaStream_t)st>>>(p);
+    latent_post_kernel<float><<<T, T < 64 ? 512 : 128, 0, (cudaStream_t)st>>>(p);
   }
   B200_CHECK_LAUNCH();
   return B200_OK;
@@ -746,6 +767,8 @@ int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int 
                              int kv_rank, float scale, int round_q, float* part, int n_split, int T, void* st) {
   B200_REQUIRE(qa && cache && slot && pos && out && T > 0 && H > 0, "lm_latent_attention: bad argument");
   if (n_split < 1 || !part) n_split = 1;
+  B200_REQUIRE(n_split <= 64, "lm_latent_attention: at most 64 splits");
+  const int vec8 = cache_bf16 && Dl % 8 == 0 && tok_stride % 8 == 0 && slot_stride % 8 == 0 && ((uintptr_t)cache & 15) == 0;
   B200_REQUIRE(kv_rank <= 1024 && kv_rank <= Dl, "lm_latent_attention: latent rank %d not supported", kv_rank);
   const int nw = H < 8 ? H : 8;
   const size_t smem = ((size_t)LA_KT * (Dl + 1) + (size_t)nw * Dl) * sizeof(float);
@@ -754,12 +777,12 @@ int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int 
   if (cache_bf16) {
     if (first_use_on_device(&g_attn_attr_bf16))
       B200_CUDA(cudaFuncSetAttribute(latent_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    LatAttnP<bf16> p{qa, ldqa, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split};
+    LatAttnP<bf16> p{qa, ldqa, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split, vec8};
     latent_attention_kernel<bf16><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   } else {
     if (first_use_on_device(&g_attn_attr_f32))
       B200_CUDA(cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    LatAttnP<float> p{qa, ldqa, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split};
+    LatAttnP<float> p{qa, ldqa, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split, 0};
     latent_attention_kernel<float><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   }
   B200_CHECK_LAUNCH();
@@ -852,7 +875,7 @@ int b200_lm_cache_transpose(const void* cache_rows, long tok_stride, int S, int 
 
 int b200_lm_argmax_rows(const float* z, long ldz, int V, int* tok, float* logprob, int B, void* st) {
   B200_REQUIRE(z && tok && B > 0 && V > 0, "lm_argmax_rows: bad argument");
-  argmax_rows_kernel<<<B, 256, 0, (cudaStream_t)st>>>(z, ldz, V, tok, logprob);
+  argmax_rows_kernel<<<B, 1024, 0, (cudaStream_t)st>>>(z, ldz, V, tok, logprob);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -101,7 +101,12 @@ class LatentAttention:
                         ctx.slot, ctx.pos, cs, self.q_rank, r, dr, self.rot_dims)
         q = ops.linear(cq, w["uq"])
         qa = ops.empty((T, H * Dl))
-        ops.gemm(q, w["ukT"], qa, M=T, N_=r, K=dn, xb=dn + dr, ldw=dn, wb=r * dn, yb=Dl, batch=H)
+        heads_tc = ops.tc_ok(T, dn, dn + dr, r) and dn % 64 == 0 and r % 64 == 0 and Dl % 4 == 0 and dv % 4 == 0
+        if heads_tc:     # a prompt: one tcgen05 product per head, overlapped (inner sizes are whole k-blocks)
+            qb = ops.to_bf16(q, H * (dn + dr))
+            ops.tc_gemm_many(qb, w["ukT"], qa, [(h * (dn + dr), h * r * dn, h * Dl, T) for h in range(H)], N_=r, K=dn, ldw=dn)
+        else:
+            ops.gemm(q, w["ukT"], qa, M=T, N_=r, K=dn, xb=dn + dr, ldw=dn, wb=r * dn, yb=Dl, batch=H)
         ops.rope_q(q, qa, cs, H, dn, dr, self.rot_dims, r)
         ol = ops.empty((T, H * r))
         segs = ctx.segments or []
@@ -115,7 +120,11 @@ class LatentAttention:
         else:
             ops.latent_attention(qa, cache_layer, ctx.slot, ctx.pos, ol, H, r, self.scale)
         att = ops.empty((T, H * dv))
-        ops.gemm(ol, w["uv"], att, M=T, N_=dv, K=r, xb=r, ldw=r, wb=dv * r, yb=dv, batch=H)
+        if heads_tc:
+            ob = ops.to_bf16(ol, H * r)
+            ops.tc_gemm_many(ob, w["uv"], att, [(h * r, h * dv * r, h * dv, T) for h in range(H)], N_=dv, K=r, ldw=r)
+        else:
+            ops.gemm(ol, w["uv"], att, M=T, N_=dv, K=r, xb=r, ldw=r, wb=dv * r, yb=dv, batch=H)
         return ops.linear(att, w["o"])
 
 
@@ -192,18 +201,17 @@ class ExpertMixture:
             counts = count.to("cpu").tolist()
         xs = ops.to_bf16(x, self.W, rows=n_all, row_map=order, div=self.top)
         hs = ops.empty((n_all, self.ff))
-        at = 0
+        seg, at = [], 0
         for e, n in enumerate(counts):
             if n:
-                ops.tc_gemm(xs[at:at + n], w["up"][e], hs[at:at + n], N_=self.ff, K=self.W)
+                seg.append((e, at, n))
             at += n
+        ops.tc_gemm_many(xs, w["up"], hs, [(a * xs.stride(0), e * self.ff * self.W, a * self.ff, n) for e, a, n in seg],
+                         N_=self.ff, K=self.W, ldw=self.W)
         hb = ops.to_bf16(hs, self.ff, relu2=True)
         ys = ops.empty((n_all, self.W))
-        at = 0
-        for e, n in enumerate(counts):
-            if n:
-                ops.tc_gemm(hb[at:at + n], w["down"][e], ys[at:at + n], N_=self.W, K=self.ff)
-            at += n
+        ops.tc_gemm_many(hb, w["down"], ys, [(a * hb.stride(0), e * self.W * self.ff, a * self.W, n) for e, a, n in seg],
+                         N_=self.W, K=self.ff, ldw=self.ff)
         out = ops.empty((n_all, self.W))
         ops.rows_scatter(ys, order, out, n_all)
         return out
