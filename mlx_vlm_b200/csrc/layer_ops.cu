@@ -299,7 +299,7 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part, in
   const float inv = inv_s;
   for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
     float a = 0.f;
-#pragma unroll 8
+#pragma unroll 16
     for (int s = 0; s < n_split; ++s) a = fmaf(pp[(long)s * row + d], wgt[s], a);
     out[(long)t * ldo + (long)h * kv_rank + d] = a * inv;
   }
@@ -650,6 +650,89 @@ __global__ void cache_transpose_kernel(const bf16* __restrict__ C, long tok_stri
   }
 }
 
+// For one to four rows (a single request decoding): the whole block works on GK_RB weight rows at once, every
+// thread owns 8 columns of a 2048-column chunk, so all loads of a block are in flight together and a product of a
+// few MB is spread over hundreds of blocks.  Sums: thread-local in k order, butterfly, then the warps in order.
+constexpr int GK_RB = 4, GK_KC = 2048;
+template <int MR>
+__global__ void __launch_bounds__(256) gemm_skinny_blk_kernel(GemmRowsP p) {
+  __shared__ __align__(16) float xs[MR][GK_KC];
+  __shared__ float red[8][GK_RB][MR];
+  __shared__ int xrow[MR], yrow[MR];
+  const int b = blockIdx.z;
+  const int rows = min(p.count ? p.count[b] : p.M, MR);
+  if (rows <= 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x < MR) {
+    int xr = -1, yr = -1;
+    if ((int)threadIdx.x < rows) {
+      if (p.list) { const int e = p.list[(long)b * p.list_stride + threadIdx.x]; xr = e / p.x_div; yr = e; }
+      else { xr = yr = threadIdx.x; }
+    }
+    xrow[threadIdx.x] = xr; yrow[threadIdx.x] = yr;
+  }
+  const float* X = p.X + (long)b * p.xb;
+  const bf16* W = p.W + (long)b * p.wb;
+  const int n0 = blockIdx.x * GK_RB;
+  float acc[GK_RB][MR];
+#pragma unroll
+  for (int r = 0; r < GK_RB; ++r)
+#pragma unroll
+    for (int i = 0; i < MR; ++i) acc[r][i] = 0.f;
+  for (int k0 = 0; k0 < p.K; k0 += GK_KC) {
+    const int kc = min(GK_KC, p.K - k0);
+    const int k = threadIdx.x * 8;
+    uint4 wv[GK_RB];
+#pragma unroll
+    for (int r = 0; r < GK_RB; ++r)          // the weight loads go out first: they are the long-latency ones
+      wv[r] = (k < kc && n0 + r < p.N) ? ldg_stream(W + (long)(n0 + r) * p.ldw + k0 + k) : make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < MR * (kc >> 2); e += blockDim.x) {
+      const int i = e / (kc >> 2), kk = (e % (kc >> 2)) << 2;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (xrow[i] >= 0) {
+        v = *reinterpret_cast<const float4*>(X + (long)xrow[i] * p.ldx + k0 + kk);
+        if (p.round_x) { v.x = rbf(v.x); v.y = rbf(v.y); v.z = rbf(v.z); v.w = rbf(v.w); }
+      }
+      *reinterpret_cast<float4*>(&xs[i][kk]) = v;
+    }
+    __syncthreads();
+    if (k < kc) {
+#pragma unroll
+      for (int r = 0; r < GK_RB; ++r) {
+        float w[8];
+        unpack8(wv[r], w);
+#pragma unroll
+        for (int i = 0; i < MR; ++i) {
+          const float4 a = *reinterpret_cast<const float4*>(&xs[i][k]);
+          const float4 c = *reinterpret_cast<const float4*>(&xs[i][k + 4]);
+          float t = acc[r][i];
+          t = fmaf(a.x, w[0], t); t = fmaf(a.y, w[1], t); t = fmaf(a.z, w[2], t); t = fmaf(a.w, w[3], t);
+          t = fmaf(c.x, w[4], t); t = fmaf(c.y, w[5], t); t = fmaf(c.z, w[6], t); t = fmaf(c.w, w[7], t);
+          acc[r][i] = t;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < GK_RB; ++r)
+#pragma unroll
+    for (int i = 0; i < MR; ++i) {
+      const float v = warp_sum(acc[r][i]);
+      if (lane == 0) red[warp][r][i] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < GK_RB * MR) {
+    const int r = threadIdx.x / MR, i = threadIdx.x % MR, n = n0 + r;
+    float v = 0.f;
+    for (int w = 0; w < 8; ++w) v += red[w][r][i];
+    if (n < p.N && yrow[i] >= 0) {
+      if (p.bias) v += bf2f(p.bias[n]);
+      (p.Y + (long)b * p.yb)[(long)yrow[i] * p.ldy + n] = gemm_epi(v, p.epi, p.epi_param);
+    }
+  }
+}
+
 // greedy pick per row: lowest index of the largest logit, and its log-probability
 __global__ void argmax_rows_kernel(const float* __restrict__ z, long ldz, int V, int* __restrict__ tok,
                                    float* __restrict__ logprob) {
@@ -787,7 +870,8 @@ int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int 
   }
   B200_CHECK_LAUNCH();
   if (n_split > 1) {
-    latent_attention_merge_kernel<<<dim3(T, H), 128, 0, (cudaStream_t)st>>>(part, n_split, kv_rank, out, ldo, H);
+    const int mt = kv_rank >= 512 ? 512 : (kv_rank + 31) / 32 * 32;
+    latent_attention_merge_kernel<<<dim3(T, H), mt, 0, (cudaStream_t)st>>>(part, n_split, kv_rank, out, ldo, H);
     B200_CHECK_LAUNCH();
   }
   return B200_OK;
@@ -819,9 +903,10 @@ int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw
   if (skinny && vec && M <= 16) {
     dim3 grid(cdiv(N, GV_WARPS * GV_R), 1, batch);
     const cudaStream_t cs = (cudaStream_t)st;
-    if (M <= 1) gemm_skinny_vec_kernel<1, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
-    else if (M <= 2) gemm_skinny_vec_kernel<2, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
-    else if (M <= 4) gemm_skinny_vec_kernel<4, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
+    dim3 gridk(cdiv(N, GK_RB), 1, batch);
+    if (M <= 1) gemm_skinny_blk_kernel<1><<<gridk, 256, 0, cs>>>(p);
+    else if (M <= 2) gemm_skinny_blk_kernel<2><<<gridk, 256, 0, cs>>>(p);
+    else if (M <= 4) gemm_skinny_blk_kernel<4><<<gridk, 256, 0, cs>>>(p);
     else if (M <= 8) gemm_skinny_vec_kernel<8, 1024><<<grid, GV_WARPS * 32, 0, cs>>>(p);
     else gemm_skinny_vec_kernel<16, 512><<<grid, GV_WARPS * 32, 0, cs>>>(p);
   } else if (skinny) {

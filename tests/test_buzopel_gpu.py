@@ -431,3 +431,42 @@ def test_batch_scheduler_lock_step_rows():
         want, margins = oracle_greedy(cfg, W, p, n)
         assert len(out[u]) == n
         same_until_tie(out[u], want, margins, f"row {u}")
+
+
+def test_trace_runner_from_a_checkpoint_folder(tmp_path):
+    """bin/trace_run on a checkpoint folder (config.json + model.safetensors, bf16 tensors with the design's names):
+    the registry picks the class from `architecture`, requests are prefilled together, decoded together, one ends
+    and a later one takes its slot; both number formats against the plain restatement"""
+    import json
+    import os
+    import subprocess
+    import sys
+    from safetensors.torch import save_file
+    cfg = config([layer(), layer(kv_from=0), layer(mlp=False)])
+    W = O.random_weights(cfg, 11)
+    model_dir = tmp_path / "model"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.contiguous() for k, v in W.items()}, str(model_dir / "model.safetensors"))
+    a, b, c = (tokens(n, cfg["vocab"], 70 + n) for n in (40, 9, 25))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}, {"id": "b", "tokens": b[:8], "want": [7]}],
+              "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[30:31], "want": [0]}, {"id": "b", "tokens": b[8:], "want": [0]}],
+              "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[31:32], "want": []}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[32:], "want": [7]}, {"id": "c", "tokens": c, "want": [0, 24]}],
+              "end": ["a", "c"]}]
+    want = {0: [(a, 0), (a, 29), (b, 7)], 1: [(a, 30), (b, 8)], 3: [(a, 39), (c, 0), (c, 24)]}
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dtype in ("bfloat16", "float32"):
+        out = tmp_path / dtype
+        r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", dtype,
+                            "--out", str(out), "--max-tokens", "80"], input="".join(json.dumps(x) + "\n" for x in steps),
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == [f"done {i}" for i in range(4)]
+        assert not (out / "2.f32").exists()
+        for st, rows in want.items():
+            got = torch.from_numpy(np.fromfile(out / f"{st}.f32", dtype="<f4").reshape(len(rows), cfg["vocab"])).double()
+            ref = torch.stack([O.forward(cfg, W, t)[i] for t, i in rows])
+            assert rel(got, ref, dtype) < TOL[dtype]
