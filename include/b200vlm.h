@@ -401,10 +401,12 @@ int b200_lm_router_topk(const float* z, long ldz, int E, int top, int* idx, floa
 int b200_lm_moe_group(const int* idx, int n_entries, int E, int* list, long list_stride, int* count, void* stream);
 /* Y[b][r][n] = epi(sum_k X[b][xr][k] W[b][n][k] + bias[n]); list/count: rows of batch b are the entries
  * list[b][0..count[b]), x row = entry / x_div, y row = entry.  epi 0 none, 1 relu^2, 2 p*tanh(v/p).
- * skinny != 0: the decode kernel (a warp per weight row). */
+ * skinny != 0: the decode kernels (weight rows streamed once for the few rows of X).  compact > 0 (skinny, with
+ * counts): at most `compact` batches have rows, and only that many slices are launched (slice z = the z-th batch
+ * whose count is not zero). */
 int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw, long wb, const void* bias, float* Y,
                       long ldy, long yb, const int* list, long list_stride, const int* count, int x_div, int M, int N,
-                      int K, int batch, int epi, float epi_param, int round_x, int skinny, void* stream);
+                      int K, int batch, int epi, float epi_param, int round_x, int skinny, int compact, void* stream);
 /* operands of the tensor-core products of a prompt step (bf16 serving mode; the products are b200_gemm_wt_f32 with
  * one bf16 part): fp32 rows -> bf16 rows zero-padded to Kp columns (gather: src row = map[i] / div; relu2: the
  * experts' activation before the rounding); fp32 rows scattered to dst_map[i]; the causal softmax of score rows

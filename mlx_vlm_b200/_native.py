@@ -120,7 +120,7 @@ LM_SIGNATURES = {
     "b200_lm_router_topk": (_I, [_P, _L, _I, _I, _P, _P, _I, _P]),
     "b200_lm_moe_group": (_I, [_P, _I, _I, _P, _L, _P, _P]),
     "b200_lm_gemm_rows": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _I,
-                               _I, _P]),
+                               _I, _I, _P]),
     "b200_lm_argmax_rows": (_I, [_P, _L, _I, _P, _P, _I, _P]),
     "b200_lm_rows_to_bf16": (_I, [_P, _L, _P, _I, _P, _L, _I, _I, _I, _I, _P]),
     "b200_gemm_wt_f32_many": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _P, _I]),

@@ -379,7 +379,30 @@ struct GemmRowsP {
   int M, N, K;
   int epi; float epi_param;              // 0 none, 1 relu^2, 2 param * tanh(v / param)
   int round_x;
-};
+  int compact, n_batch;                  // compact: blockIdx.z counts the batches that HAVE rows (count[b] > 0) —
+};                                       // a decode step launches top x rows slices, not one per expert
+// the z-th batch with rows, or -1 (whole block; the counts are read 32 at a time, not one after the other)
+__device__ __forceinline__ int nth_active(const int* __restrict__ count, int n_batch, int z) {
+  __shared__ int s_found;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int found = -1, base = 0;
+    for (int e0 = 0; e0 < n_batch && found < 0; e0 += 32) {
+      const int e = e0 + lane;
+      const unsigned m = __ballot_sync(0xffffffffu, e < n_batch && count[e] > 0);
+      const int c = __popc(m);
+      if (z < base + c) {
+        unsigned mm = m;
+        for (int i = 0; i < z - base; ++i) mm &= mm - 1;
+        found = e0 + __ffs(mm) - 1;
+      }
+      base += c;
+    }
+    if (lane == 0) s_found = found;
+  }
+  __syncthreads();
+  return s_found;
+}
 __device__ __forceinline__ float gemm_epi(float v, int epi, float param) {
   if (epi == 1) { v = fmaxf(v, 0.f); return v * v; }
   if (epi == 2) return param * tanhf(v / param);
@@ -463,7 +486,8 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmRowsP p) {
 // over the weight row; k order fixed by the lane striding + butterfly, independent of the other rows
 constexpr int GS_R = 8;
 __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmRowsP p) {
-  const int b = blockIdx.z;
+  const int b = p.compact ? nth_active(p.count, p.n_batch, blockIdx.z) : (int)blockIdx.z;
+  if (b < 0) return;
   const int rows = p.count ? p.count[b] : p.M;
   const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (n >= p.N || rows <= 0) return;
@@ -510,7 +534,8 @@ template <int MR, int GV_KC>
 __global__ void __launch_bounds__(GV_WARPS * 32) gemm_skinny_vec_kernel(GemmRowsP p) {
   __shared__ __align__(16) float xs[MR][GV_KC];
   __shared__ int xrow[MR], yrow[MR];
-  const int b = blockIdx.z;
+  const int b = p.compact ? nth_active(p.count, p.n_batch, blockIdx.z) : (int)blockIdx.z;
+  if (b < 0) return;
   const int rows = min(p.count ? p.count[b] : p.M, MR);
   if (rows <= 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -659,7 +684,8 @@ __global__ void __launch_bounds__(256) gemm_skinny_blk_kernel(GemmRowsP p) {
   __shared__ __align__(16) float xs[MR][GK_KC];
   __shared__ float red[8][GK_RB][MR];
   __shared__ int xrow[MR], yrow[MR];
-  const int b = blockIdx.z;
+  const int b = p.compact ? nth_active(p.count, p.n_batch, blockIdx.z) : (int)blockIdx.z;
+  if (b < 0) return;
   const int rows = min(p.count ? p.count[b] : p.M, MR);
   if (rows <= 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -893,20 +919,28 @@ int b200_lm_moe_group(const int* idx, int n_entries, int E, int* list, long list
 
 int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw, long wb, const void* bias, float* Y,
                       long ldy, long yb, const int* list, long list_stride, const int* count, int x_div, int M, int N,
-                      int K, int batch, int epi, float epi_param, int round_x, int skinny, void* st) {
+                      int K, int batch, int epi, float epi_param, int round_x, int skinny, int compact, void* st) {
   B200_REQUIRE(X && W && Y && M > 0 && N > 0 && K > 0 && batch > 0, "lm_gemm_rows: bad argument");
   B200_REQUIRE((list == nullptr) == (count == nullptr), "lm_gemm_rows: a row list needs its counts");
   GemmRowsP p{X, ldx, xb, (const bf16*)W, ldw, wb, (const bf16*)bias, Y, ldy, yb, list, list_stride, count,
-              x_div > 0 ? x_div : 1, M, N, K, epi, epi_param, round_x};
+              x_div > 0 ? x_div : 1, M, N, K, epi, epi_param, round_x, 0, batch};
+  if (skinny && count && compact > 0 && compact < batch) {   // at most `compact` batches can have rows
+    p.compact = 1;
+    batch = compact;
+  }
   const bool vec = K % 8 == 0 && ldw % 8 == 0 && wb % 8 == 0 && ldx % 4 == 0 && xb % 4 == 0 &&
                    ((uintptr_t)W & 15) == 0 && ((uintptr_t)X & 15) == 0;
   if (skinny && vec && M <= 16) {
     dim3 grid(cdiv(N, GV_WARPS * GV_R), 1, batch);
     const cudaStream_t cs = (cudaStream_t)st;
     dim3 gridk(cdiv(N, GK_RB), 1, batch);
-    if (M <= 1) gemm_skinny_blk_kernel<1><<<gridk, 256, 0, cs>>>(p);
-    else if (M <= 2) gemm_skinny_blk_kernel<2><<<gridk, 256, 0, cs>>>(p);
-    else if (M <= 4) gemm_skinny_blk_kernel<4><<<gridk, 256, 0, cs>>>(p);
+    const bool one_chunk = K <= GK_KC;     // measured: the block-wide kernel wins while a weight row is one chunk
+    if (M <= 1 && one_chunk) gemm_skinny_blk_kernel<1><<<gridk, 256, 0, cs>>>(p);
+    else if (M <= 2 && one_chunk) gemm_skinny_blk_kernel<2><<<gridk, 256, 0, cs>>>(p);
+    else if (M <= 4 && one_chunk) gemm_skinny_blk_kernel<4><<<gridk, 256, 0, cs>>>(p);
+    else if (M <= 1) gemm_skinny_vec_kernel<1, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
+    else if (M <= 2) gemm_skinny_vec_kernel<2, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
+    else if (M <= 4) gemm_skinny_vec_kernel<4, 2048><<<grid, GV_WARPS * 32, 0, cs>>>(p);
     else if (M <= 8) gemm_skinny_vec_kernel<8, 1024><<<grid, GV_WARPS * 32, 0, cs>>>(p);
     else gemm_skinny_vec_kernel<16, 512><<<grid, GV_WARPS * 32, 0, cs>>>(p);
   } else if (skinny) {

@@ -182,10 +182,10 @@ class ExpertMixture:
             return self._experts_prompt(ops, x, lists, count), wgt
         hid = ops.empty((T * self.top, self.ff))
         ops.gemm(x, w["up"], hid, M=T, N_=self.ff, K=self.W, wb=self.ff * self.W, batch=self.E, lists=lists,
-                 count=count, x_div=self.top, epi=EPI_RELU2)
+                 count=count, x_div=self.top, epi=EPI_RELU2, compact=min(self.E, T * self.top))
         out = ops.empty((T * self.top, self.W))
         ops.gemm(hid, w["down"], out, M=T, N_=self.W, K=self.ff, wb=self.W * self.ff, batch=self.E, lists=lists,
-                 count=count, x_div=1)
+                 count=count, x_div=1, compact=min(self.E, T * self.top))
         return out, wgt
 
 

@@ -129,13 +129,14 @@ class LayerOps:
         return lists, count
 
     def gemm(self, X, W, Y, *, M, N_, K, ldx=None, xb=0, ldw=None, wb=0, ldy=None, yb=0, batch=1, bias=None,
-             lists=None, count=None, x_div=1, epi=EPI_NONE, epi_param=0.0):
-        """Y[b][r][:] = epi(X[b][r'] . W[b]^T + bias); strides in elements (default: the tensors' own rows)"""
+             lists=None, count=None, x_div=1, epi=EPI_NONE, epi_param=0.0, compact=0):
+        """Y[b][r][:] = epi(X[b][r'] . W[b]^T + bias); strides in elements (default: the tensors' own rows).
+        compact: an upper bound of the batches that have rows (a decode step: rows x top experts of many)"""
         self._ok(self.lib.b200_lm_gemm_rows(
             X.data_ptr(), X.stride(0) if ldx is None else ldx, xb, W.data_ptr(), K if ldw is None else ldw, wb,
             N.ptr(bias), Y.data_ptr(), Y.stride(0) if ldy is None else ldy, yb, N.ptr(lists),
             lists.stride(0) if lists is not None else 0, N.ptr(count), x_div, M, N_, K, batch, epi, float(epi_param),
-            int(not self.exact), int(M <= SKINNY_ROWS), self.s), "lm_gemm_rows")
+            int(not self.exact), int(M <= SKINNY_ROWS), int(compact), self.s), "lm_gemm_rows")
 
     # ---- the tensor-core path of prompt steps (bf16 serving mode) ----------------------------------------
     def tc_ok(self, rows: int, *ks: int) -> bool:
