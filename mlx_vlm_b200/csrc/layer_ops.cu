@@ -190,8 +190,11 @@ template <typename CT>
 __global__ void latent_attention_kernel(LatAttnP<CT> p) {
   extern __shared__ float sm[];
   const int t = blockIdx.x, hg = blockIdx.y, nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int Dl = p.Dl, ldk = Dl + 1;
-  float* keys = sm;                       // [LA_KT][Dl + 1]
+  // rows of 4n numbers are padded by 4 (16-byte rows for 128-bit shared loads: a quarter warp's eight rows then
+  // fall on all 32 banks), other rows by 1
+  const bool v4 = (p.Dl & 3) == 0;
+  const int Dl = p.Dl, ldk = Dl + (v4 ? 4 : 1);
+  float* keys = sm;                       // [LA_KT][ldk]
   float* qs = sm + LA_KT * ldk;           // [nw][Dl]
   const int h = hg * nw + warp;
   const bool live = h < p.H;
@@ -215,8 +218,8 @@ __global__ void latent_attention_kernel(LatAttnP<CT> p) {
         const int j = e / per_row, i = (e - j * per_row) << 3;
         float f[8];
         unpack8(*reinterpret_cast<const uint4*>(base + (long)(k0 + j) * p.tok_stride + i), f);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) keys[j * ldk + i + u] = f[u];
+        *reinterpret_cast<float4*>(&keys[j * ldk + i]) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(&keys[j * ldk + i + 4]) = make_float4(f[4], f[5], f[6], f[7]);
       }
     } else {
       for (int e = threadIdx.x; e < nk * Dl; e += blockDim.x) {
@@ -231,7 +234,18 @@ __global__ void latent_attention_kernel(LatAttnP<CT> p) {
       const float* kr = keys + lane * ldk;
       const float* qr = qs + warp * Dl;
       float a = 0.f;
-      for (int i = 0; i < Dl; ++i) a = fmaf(qr[i], kr[i], a);
+      if (v4) {                              // fixed order: four running sums over i mod 4, then (0 + 1) + (2 + 3)
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+        for (int i = 0; i < Dl; i += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
+          a0 = fmaf(q4.x, k4.x, a0); a1 = fmaf(q4.y, k4.y, a1); a2 = fmaf(q4.z, k4.z, a2); a3 = fmaf(q4.w, k4.w, a3);
+        }
+        a = (a0 + a1) + (a2 + a3);
+      } else {
+        for (int i = 0; i < Dl; ++i) a = fmaf(qr[i], kr[i], a);
+      }
       s = a * p.scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -880,7 +894,7 @@ int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int 
   const int vec8 = cache_bf16 && Dl % 8 == 0 && tok_stride % 8 == 0 && slot_stride % 8 == 0 && ((uintptr_t)cache & 15) == 0;
   B200_REQUIRE(kv_rank <= 1024 && kv_rank <= Dl, "lm_latent_attention: latent rank %d not supported", kv_rank);
   const int nw = H < 8 ? H : 8;
-  const size_t smem = ((size_t)LA_KT * (Dl + 1) + (size_t)nw * Dl) * sizeof(float);
+  const size_t smem = ((size_t)LA_KT * (Dl + ((Dl & 3) == 0 ? 4 : 1)) + (size_t)nw * Dl) * sizeof(float);
   B200_REQUIRE(smem <= 200 * 1024, "lm_latent_attention: rows of %d numbers do not fit shared memory", Dl);
   dim3 grid(T, cdiv(H, nw), n_split);
   if (cache_bf16) {

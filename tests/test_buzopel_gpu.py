@@ -207,12 +207,13 @@ def _attend(eng, cache, q, slot, pos, H, r, scale):
     return host(eng, out).view(q.shape[0], H, r)
 
 
-def test_attention_far_key_and_tile_edges():
+@pytest.mark.parametrize("r,dr", [(12, 4), (13, 2)])
+def test_attention_far_key_and_tile_edges(r, dr):
     """the kernel stages keys 32 at a time: a key that stands out is found wherever it lies (first row, last of a
     tile, first of the next, far back among hundreds), the row just past the query's position is never seen, and
     the result matches a plain softmax"""
     eng = _ops()
-    H, r, dr, S = 2, 12, 4, 700
+    H, S = 2, 700          # rows of 16 numbers (128-bit shared loads) and of 15 (the scalar path)
     g = torch.Generator().manual_seed(3)
     rows = torch.nn.functional.normalize(torch.randn(2, S, r + dr, generator=g), dim=-1)   # a row's best match is itself
     cache = dev(rows)
