@@ -87,6 +87,10 @@ class LayerEngine:
                 embeds: Optional[torch.Tensor] = None, segments=None) -> torch.Tensor:
         """tokens / slot / pos: (T,) int32 device.  want: (n,) int32 device rows whose logits are wanted (None:
         every row).  Returns fp32 logits (n, vocab).  The cache rows of the tokens are written on the way."""
+        with self.ops.on_stream():
+            return self._forward(tokens, slot, pos, want, embeds, segments)
+
+    def _forward(self, tokens, slot, pos, want, embeds, segments):
         c, ops = self.core, self.ops
         ctx = StepCtx(ops, slot, pos, self.pool, c.eps, segments)    # segments: the host's view of a prompt step
         if embeds is not None:

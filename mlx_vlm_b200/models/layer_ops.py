@@ -30,6 +30,7 @@ class LayerOps:
         self.device, self.stream, self.exact = torch.device(device), stream, bool(exact)
         self.launches = 0
         self._inv_freq = {}
+        self._on_stream = False
         self._side = None             # side streams for many small independent products (experts, heads)
         self._tuned = set()           # product classes whose configuration the GEMM has already measured
 
@@ -46,8 +47,26 @@ class LayerOps:
         N.check(rc, what, self.lib)
 
     def empty(self, shape, dtype=torch.float32) -> torch.Tensor:
+        if self._on_stream:       # the caller already made the engine's stream current (one context per step,
+            return torch.empty(shape, dtype=dtype, device=self.device)   # not one per buffer: ~10 us each)
         with torch.cuda.stream(self.stream):
             return torch.empty(shape, dtype=dtype, device=self.device)
+
+    def on_stream(self):
+        """context: the engine's stream is current for everything inside (buffers of a step come from its pool)"""
+        ops = self
+
+        class _Ctx:
+            def __enter__(self):
+                self.inner = torch.cuda.stream(ops.stream)
+                self.inner.__enter__()
+                self.prev, ops._on_stream = ops._on_stream, True
+
+            def __exit__(self, *exc):
+                ops._on_stream = self.prev
+                return self.inner.__exit__(*exc)
+
+        return _Ctx()
 
     def to_device(self, arr, dtype=np.int32) -> torch.Tensor:
         t = torch.from_numpy(np.ascontiguousarray(arr, dtype=dtype)).pin_memory()
