@@ -17,6 +17,7 @@ from typing import Dict, List, Optional
 
 import torch
 
+from .._native import B200Error as _B200Error
 from .layer_ops import EPI_RELU2, LayerOps
 
 
@@ -103,27 +104,41 @@ class LatentAttention:
         qa = ops.empty((T, H * Dl))
         heads_tc = ops.tc_ok(T, dn, dn + dr, r) and dn % 64 == 0 and r % 64 == 0 and Dl % 4 == 0 and dv % 4 == 0
         if heads_tc:     # a prompt: one tcgen05 product per head, overlapped (inner sizes are whole k-blocks)
-            qb = ops.to_bf16(q, H * (dn + dr))
-            ops.tc_gemm_many(qb, w["ukT"], qa, [(h * (dn + dr), h * r * dn, h * Dl, T) for h in range(H)], N_=r, K=dn, ldw=dn)
-        else:
+            try:
+                qb = ops.to_bf16(q, H * (dn + dr))
+                ops.tc_gemm_many(qb, w["ukT"], qa, [(h * (dn + dr), h * r * dn, h * Dl, T) for h in range(H)], N_=r, K=dn,
+                                 ldw=dn)
+            except _B200Error as e:
+                ops.tc_refused(e)
+                heads_tc = False
+        if not heads_tc:
             ops.gemm(q, w["ukT"], qa, M=T, N_=r, K=dn, xb=dn + dr, ldw=dn, wb=r * dn, yb=Dl, batch=H)
         ops.rope_q(q, qa, cs, H, dn, dr, self.rot_dims, r)
         ol = ops.empty((T, H * r))
         segs = ctx.segments or []
+        done = False
         if any(ops.tc_ok(n, Dl, r, cache_layer.stride(1)) for _, n, _, _ in segs) and cache_layer.dtype == torch.bfloat16:
-            for start, n, slot, p0 in segs:          # long portions on the tensor cores, the rest on the row kernel
-                sl = slice(start, start + n)
-                if ops.tc_ok(n, Dl, r, cache_layer.stride(1)):
-                    self._attend_prompt(ops, qa[sl], cache_layer[slot], ctx.pos[sl], ol[sl], p0 + n)
-                else:
-                    ops.latent_attention(qa[sl], cache_layer, ctx.slot[sl], ctx.pos[sl], ol[sl], H, r, self.scale)
-        else:
+            try:
+                for start, n, slot, p0 in segs:      # long portions on the tensor cores, the rest on the row kernel
+                    sl = slice(start, start + n)
+                    if ops.tc_ok(n, Dl, r, cache_layer.stride(1)):
+                        self._attend_prompt(ops, qa[sl], cache_layer[slot], ctx.pos[sl], ol[sl], p0 + n)
+                    else:
+                        ops.latent_attention(qa[sl], cache_layer, ctx.slot[sl], ctx.pos[sl], ol[sl], H, r, self.scale)
+                done = True
+            except _B200Error as e:
+                ops.tc_refused(e)
+        if not done:
             ops.latent_attention(qa, cache_layer, ctx.slot, ctx.pos, ol, H, r, self.scale)
         att = ops.empty((T, H * dv))
         if heads_tc:
-            ob = ops.to_bf16(ol, H * r)
-            ops.tc_gemm_many(ob, w["uv"], att, [(h * r, h * dv * r, h * dv, T) for h in range(H)], N_=dv, K=r, ldw=r)
-        else:
+            try:
+                ob = ops.to_bf16(ol, H * r)
+                ops.tc_gemm_many(ob, w["uv"], att, [(h * r, h * dv * r, h * dv, T) for h in range(H)], N_=dv, K=r, ldw=r)
+            except _B200Error as e:
+                ops.tc_refused(e)
+                heads_tc = False
+        if not heads_tc:
             ops.gemm(ol, w["uv"], att, M=T, N_=dv, K=r, xb=r, ldw=r, wb=dv * r, yb=dv, batch=H)
         return ops.linear(att, w["o"])
 
@@ -179,7 +194,10 @@ class ExpertMixture:
         idx, wgt = ops.router_topk(z, self.top)
         lists, count = ops.moe_group(idx, self.E)
         if ops.tc_ok(T, self.W, self.ff):
-            return self._experts_prompt(ops, x, lists, count), wgt
+            try:
+                return self._experts_prompt(ops, x, lists, count), wgt
+            except _B200Error as e:
+                ops.tc_refused(e)
         hid = ops.empty((T * self.top, self.ff))
         ops.gemm(x, w["up"], hid, M=T, N_=self.ff, K=self.W, wb=self.ff * self.W, batch=self.E, lists=lists,
                  count=count, x_div=self.top, epi=EPI_RELU2, compact=min(self.E, T * self.top))

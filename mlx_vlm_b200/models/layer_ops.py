@@ -31,6 +31,7 @@ class LayerOps:
         self.launches = 0
         self._inv_freq = {}
         self._on_stream = False
+        self.tc_enabled = True
         self._side = None             # side streams for many small independent products (experts, heads)
         self._tuned = set()           # product classes whose configuration the GEMM has already measured
 
@@ -91,6 +92,8 @@ class LayerOps:
 
     def rope_table(self, pos: torch.Tensor, base: float, dims: int) -> torch.Tensor:
         T, half = pos.shape[0], dims // 2
+        if half == 0:             # nothing is rotated: the kernels never read the table
+            return self.empty((1, 1, 2))
         cs = self.empty((T, half, 2))
         self._ok(self.lib.b200_lm_rope_table(pos.data_ptr(), self.inv_freq(base, dims).data_ptr(), cs.data_ptr(), T,
                                              half, self.s), "lm_rope_table")
@@ -161,7 +164,15 @@ class LayerOps:
     def tc_ok(self, rows: int, *ks: int) -> bool:
         """a product with `rows` rows and inner sizes `ks` may run on the tcgen05 GEMM: serving mode, enough rows
         to fill a tile, 16-byte rows for the TMA"""
-        return (not self.exact) and rows >= TC_MIN_ROWS and all(k % 8 == 0 for k in ks)
+        return self.tc_enabled and (not self.exact) and rows >= TC_MIN_ROWS and all(k % 8 == 0 for k in ks)
+
+    def tc_refused(self, err: Exception):
+        """the tensor-core GEMM rejected a product's arguments (its checks run before any launch): say so once and
+        keep to the general row kernels — still this library's CUDA path — from here on"""
+        if self.tc_enabled:
+            import sys
+            print(f"layer ops: tensor-core path switched off, the row kernels take over ({err})", file=sys.stderr)
+        self.tc_enabled = False
 
     def to_bf16(self, X: torch.Tensor, K: int, rows: Optional[int] = None, row_map: Optional[torch.Tensor] = None,
                 div: int = 1, relu2: bool = False) -> torch.Tensor:
@@ -249,9 +260,12 @@ class LayerOps:
         (T, K), n = X.shape, W.shape[0]
         Y = self.empty((T, n))
         if epi == EPI_NONE and self.tc_ok(T, K):
-            self.tc_gemm(self.to_bf16(X, K), W, Y, N_=n, K=K, bias=bias)
-        else:
-            self.gemm(X, W, Y, M=T, N_=n, K=K, bias=bias, epi=epi, epi_param=epi_param)
+            try:
+                self.tc_gemm(self.to_bf16(X, K), W, Y, N_=n, K=K, bias=bias)
+                return Y
+            except N.B200Error as e:
+                self.tc_refused(e)
+        self.gemm(X, W, Y, M=T, N_=n, K=K, bias=bias, epi=epi, epi_param=epi_param)
         return Y
 
     def argmax_rows(self, z, tok, logprob=None):

@@ -37,7 +37,7 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print("trace_run: no CUDA device (there is no CPU path)", file=sys.stderr)
         return 2
-    model = load_model(a.model, dtype=a.dtype)
+    model = load_model(a.model, dtype=a.dtype, strict=False)     # tensors the configuration does not name are ignored
     lm = model.language_model
     if not hasattr(lm, "step"):
         print(f"trace_run: {type(model).__module__} has no token-level step function", file=sys.stderr)

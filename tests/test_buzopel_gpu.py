@@ -351,6 +351,32 @@ def test_long_prompt_paths_of_the_serving_mode():
     assert rel(both[:200], ref[:200], "bfloat16") < TOL["bfloat16"] and rel(both[200:], ref[:30], "bfloat16") < TOL["bfloat16"]
 
 
+def test_row_kernels_take_over_when_the_tensor_core_gemm_refuses():
+    """a product whose arguments the tcgen05 GEMM rejects (its checks run before any launch) is redone on the row
+    kernels and the tensor-core path stays off: same logits within the serving mode's noise"""
+    from mlx_vlm_b200 import _native
+    cfg = config([layer(), layer(kv_from=0)])
+    model, W = build(cfg, "bfloat16", seed=5)
+    ops = model.engine.ops
+    toks = tokens(160, cfg["vocab"], 12)
+    ref = O.forward(cfg, W, toks)
+    real, calls = ops.tc_gemm, []
+
+    def refuse(*a, **k):
+        calls.append(1)
+        raise _native.B200Error("refused for the test")
+
+    ops.tc_gemm = refuse
+    try:
+        got = run_alone(model, toks)
+    finally:
+        ops.tc_gemm = real
+    assert calls and not ops.tc_enabled
+    assert rel(got, ref, "bfloat16") < TOL["bfloat16"]
+    ops.tc_enabled = True
+    assert rel(run_alone(model, toks), ref, "bfloat16") < TOL["bfloat16"]
+
+
 def test_long_decoding():
     cfg = config(layers=[layer(), layer(kv_from=0)])
     model, W = build(cfg)
@@ -366,6 +392,7 @@ OTHER = {
     "layers of different sizes": config([layer(kv_rank=40, rot=8), layer(kv_rank=24, rot=16, heads=2, base=100.0),
                                          layer(kv_from=0), layer(kv_from=1, heads=2, kv_rank=24, rot=16, base=100.0,
                                                                  mlp=False)], eps=1e-3),
+    "nothing rotated": config([layer(rot=0), layer(rot=0, kv_from=0)]),
     "equal sizes": config([layer(heads=2, dim=32, rot=32, vdim=32, kv_rank=32, q_rank=32, experts=4, top=4, ff=32)],
                           width=32, vocab=32),
 }
