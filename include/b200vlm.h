@@ -320,6 +320,11 @@ int b200_f32_gather_rows(const float* in, long ld_in, const int* idx, int n_idx,
 int b200_gemm_wt_f32(const void* X, long ldx, const void* W, long ldw, const void* bias, const float* res32,
                      long ldr32, float* C32, long ldc32, void* Csplit, long ld_split, int n_pad, int T, int N,
                      int K_w, int n_parts, int epilogue, int mode, void* stream);
+/* grouped Linear in ONE launch: token tile y (128 rows) of X [n_tiles * 128, ceil64(K_w)] bf16 multiplies the weight
+ * rows of group tile_group[y] (device; < 0: empty tile) of W [n_groups][N][K_w]; C32 [n_tiles * 128, N] fp32.  The groups'
+ * rows lie in segments padded to whole tiles (b200_lm_moe_tiles builds the table on the device) */
+int b200_gemm_wt_f32_grouped(const void* X, long ldx, const void* W, long ldw, float* C32, long ldc32,
+                             const int* tile_group, int n_tiles, int n_groups, int N, int K_w, void* stream);
 /* many independent small Linears of one shape family in one call (a mixture's experts over their token segments, the
  * heads of a per-head projection): product i is C32 + c_off[i] [rows[i], N] = (X + x_off[i]) . (W + w_off[i])^T, one
  * bf16 part, offsets in elements, launched round-robin on `streams` (ordered by the caller's events) */
@@ -417,6 +422,10 @@ int b200_lm_rows_to_bf16(const float* X, long ldx, const int* map, int div, void
 int b200_lm_rows_scatter(const float* X, long ldx, const int* dst_map, float* out, long ldo, int T, int K, void* stream);
 /* order[sum(count[0..e)) + i] = list[e][i]: the (token, choice) entries sorted by expert */
 int b200_lm_moe_order(const int* list, long list_stride, const int* count, int E, int* order, void* stream);
+/* the entries sorted by expert in segments padded to whole tiles of `tile` rows (order: -1 in the padding and past the
+ * last segment; n_rows % tile == 0) and the expert of every tile (-1 past the last segment) */
+int b200_lm_moe_tiles(const int* list, long list_stride, const int* count, int E, int tile, int* order, int n_rows,
+                      int* tile_group, void* stream);
 int b200_lm_masked_softmax_bf16(const float* S, long lds, const int* pos, int H, float scale, void* P, long ldp,
                                 int rows, int Sp, void* stream);
 int b200_lm_cache_transpose(const void* cache_rows, long tok_stride, int S, int Sp, int kv_rank, void* out, void* stream);

@@ -191,6 +191,11 @@ struct WtExt {
   bf16* Csplit;      // B200_WT_SPLIT output [hi | lo]
   long ld_split;
   int n_pad;         // columns between the hi and the lo half
+  // grouped products (the experts of a mixture over token segments padded to whole token tiles): token tile y uses the
+  // weight rows of group tile_group[y] (device array; < 0: the tile is empty and its CTAs leave at once); W holds
+  // n_groups x N rows.  Launched plainly (no programmatic dependent launch): the table is read at the top of the kernel.
+  const int* tile_group = nullptr;
+  int n_groups = 0;
 };
 void gemm_wt_auto(int T, int row_blocks, int K, bool allow_split, WtConfig* c, int sm_count);
 int gemm_wt(const void* X, long ldx, const void* W, const void* bias, const void* residual, long ldr,

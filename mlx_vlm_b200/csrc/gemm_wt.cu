@@ -65,6 +65,7 @@ struct WtParams {
   bf16* Csplit;      // B200_WT_SPLIT: output written as [hi | lo] bf16 halves, n_pad columns apart
   long ld_split;
   int n_pad;
+  const int* tile_group;  // grouped products: token tile y multiplies the weight rows of group tile_group[y] (< 0: empty)
 };
 
 __device__ __forceinline__ uint32_t w_smem_u32(const void* p) {
@@ -192,6 +193,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int rb = blockIdx.x;
   const int n0 = rb * (swiglu ? 64 : WT_ROWS);  // first output feature (SwiGLU: channel) of the tile
   const int t0 = blockIdx.y * p.TN;
+  int n0w = n0;                                 // first weight row of the tile (grouped: inside the tile's group)
+  if (p.tile_group) {
+    const int g = p.tile_group[blockIdx.y];
+    if (g < 0) return;                          // an empty token tile: nothing is allocated yet
+    n0w += g * p.N;
+  }
   const int split = blockIdx.z;
   const int kb_total = (p.K + WT_BK - 1) / WT_BK;
   const int kb0 = split * p.kb_per_split;
@@ -221,7 +228,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         w_tma_2d(sW + j * WT_WBLK, &tmW, &full_bar[s], kc, n0);
         w_tma_2d(sW + j * WT_WBLK + 64 * 128, &tmW, &full_bar[s], kc, p.inter + n0);
       } else {
-        w_tma_2d(sW + j * WT_WBLK, &tmW, &full_bar[s], kc, n0);
+        w_tma_2d(sW + j * WT_WBLK, &tmW, &full_bar[s], kc, n0w);
       }
     }
   };
@@ -789,13 +796,18 @@ int gemm_wt(const void* X, long ldx, const void* W, const void* bias, const void
     p.kb_w = ext->kb_w; p.C32 = ext->C32; p.res32 = ext->res32; p.ldc32 = ext->ldc32; p.ldr32 = ext->ldr32;
     p.Csplit = ext->Csplit; p.ld_split = ext->ld_split; p.n_pad = ext->n_pad;
     if (ext->kb_w > 0) k_w = ext->k_w;
+    p.tile_group = ext->tile_group;
   }
+  const bool grouped = ext && ext->tile_group;
+  B200_REQUIRE(!grouped || (mode == B200_WT_F32 && ext->n_groups > 0 && cfg.split == 1 && !bias),
+               "gemm_wt: grouped products are fp32-output, unsplit, without bias");
   const int stage = cfg.KS * (WT_WBLK + cfg.TN * 128);
   const size_t smem = (size_t)cfg.stages * stage + 1024;
   B200_REQUIRE(smem <= 227 * 1024 - 1024, "gemm_wt: %zu B of shared memory", smem);
   B200_REQUIRE((size_t)cfg.stages * stage >= (size_t)WT_EPI_TOK * WT_ROWS * 4, "gemm_wt: ring smaller than the epilogue staging tile");
   CUtensorMap tw, tx;
-  int rc = wt_tmap(W, (long)(ext && ext->ldw > 0 ? ext->ldw : k_w), N, k_w, mode == B200_WT_SWIGLU ? 64 : WT_ROWS, &tw);
+  int rc = wt_tmap(W, (long)(ext && ext->ldw > 0 ? ext->ldw : k_w), grouped ? ext->n_groups * N : N, k_w,
+                   mode == B200_WT_SWIGLU ? 64 : WT_ROWS, &tw);
   if (rc) return rc;
   if ((rc = wt_tmap(X, ldx, T, K, cfg.TN, &tx))) return rc;
   static unsigned long long set_mask = 0ull;
@@ -820,7 +832,7 @@ int gemm_wt(const void* X, long ldx, const void* W, const void* bias, const void
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
-  lc.numAttrs = g_wt_pdl ? 1 : 0;
+  lc.numAttrs = (g_wt_pdl && !grouped) ? 1 : 0;
   if (mode == B200_WT_F32 || mode == B200_WT_SPLIT) {
     B200_CUDA(cudaLaunchKernelEx(&lc, gemm_wt_kernel<true>, tw, tx, p));
   } else {

@@ -629,9 +629,10 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemm_skinny_vec_kernel(GemmRows
 __global__ void rows_to_bf16_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ map, int div,
                                     bf16* __restrict__ out, long ldo, int K, int Kp, int relu2) {
   const int i = blockIdx.x;
-  const float* x = X + (long)(map ? map[i] / div : i) * ldx;
+  const int src = map ? map[i] : i;            // a negative entry of the map: a padding row, written as zeros
+  const float* x = X + (long)(src < 0 ? 0 : (map ? src / div : src)) * ldx;
   for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
-    float v = k < K ? x[k] : 0.f;
+    float v = (k < K && src >= 0) ? x[k] : 0.f;
     if (relu2) { v = fmaxf(v, 0.f); v *= v; }
     out[(long)i * ldo + k] = f2bf(v);
   }
@@ -639,6 +640,7 @@ __global__ void rows_to_bf16_kernel(const float* __restrict__ X, long ldx, const
 __global__ void rows_scatter_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ dst_map,
                                     float* __restrict__ out, long ldo, int K) {
   const int i = blockIdx.x;
+  if (dst_map[i] < 0) return;                  // a padding row
   const float* x = X + (long)i * ldx;
   float* o = out + (long)dst_map[i] * ldo;
   for (int k = threadIdx.x; k < K; k += blockDim.x) o[k] = x[k];
@@ -651,6 +653,26 @@ __global__ void moe_order_kernel(const int* __restrict__ list, long list_stride,
   for (int i = 0; i < e; ++i) base += count[i];
   const int n = count[e];
   for (int i = threadIdx.x; i < n; i += blockDim.x) order[base + i] = list[(long)e * list_stride + i];
+}
+// entries sorted by expert in segments padded to whole token tiles of `tile` rows: order[seg(e) + i] = list[e][i],
+// -1 in the padding and past the last segment; tile_group[y] = the expert of tile y, -1 past the last segment
+__global__ void moe_tiles_kernel(const int* __restrict__ list, long list_stride, const int* __restrict__ count, int E,
+                                 int tile, int* __restrict__ order, int n_rows, int* __restrict__ tile_group) {
+  const int e = blockIdx.x;
+  int base = 0, total = 0;
+  for (int i = 0; i < E; ++i) {
+    const int padded = (count[i] + tile - 1) / tile * tile;
+    if (i < e) base += padded;
+    total += padded;
+  }
+  if (e < E) {
+    const int n = count[e], padded = (n + tile - 1) / tile * tile;
+    for (int i = threadIdx.x; i < padded; i += blockDim.x) order[base + i] = i < n ? list[(long)e * list_stride + i] : -1;
+    for (int y = threadIdx.x; y < padded / tile; y += blockDim.x) tile_group[base / tile + y] = e;
+  } else {                                    // the extra block: everything past the last segment
+    for (int i = total + threadIdx.x; i < n_rows; i += blockDim.x) order[i] = -1;
+    for (int y = total / tile + threadIdx.x; y < n_rows / tile; y += blockDim.x) tile_group[y] = -1;
+  }
 }
 // causal softmax of score rows: row r belongs to query r / H at position pos[r / H], which sees keys 0..pos;
 // P (bf16, normalised in fp32 before the rounding) is zero past the last visible key and in the padding
@@ -986,6 +1008,14 @@ int b200_lm_rows_scatter(const float* X, long ldx, const int* dst_map, float* ou
 int b200_lm_moe_order(const int* list, long list_stride, const int* count, int E, int* order, void* st) {
   B200_REQUIRE(list && count && order && E > 0, "lm_moe_order: bad argument");
   moe_order_kernel<<<E, 256, 0, (cudaStream_t)st>>>(list, list_stride, count, order);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_moe_tiles(const int* list, long list_stride, const int* count, int E, int tile, int* order, int n_rows,
+                      int* tile_group, void* st) {
+  B200_REQUIRE(list && count && order && tile_group && E > 0 && tile > 0 && n_rows % tile == 0, "lm_moe_tiles: bad argument");
+  moe_tiles_kernel<<<E + 1, 256, 0, (cudaStream_t)st>>>(list, list_stride, count, E, tile, order, n_rows, tile_group);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

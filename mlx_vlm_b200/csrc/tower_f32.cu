@@ -649,6 +649,22 @@ int b200_gemm_wt_f32(const void* X, long ldx, const void* W, long ldw, const voi
   return gemm_wt_tuned(X, ldx, W, bias, nullptr, 0, nullptr, 0, nullptr, 0, T, N, n_parts * kbw * 64, epilogue, mode, 0,
                        false, 148, nullptr, (cudaStream_t)stream, &ext);
 }
+/* Grouped Linear on the tensor cores, ONE launch: token tile y (128 rows of X, C32) multiplies the weight rows of group
+ * tile_group[y] (device array of n_tiles entries; < 0: an empty tile).  X [n_tiles * 128, ceil64(K_w)] bf16 holds every
+ * group's rows in a segment padded to whole tiles, W [n_groups][N][K_w] bf16, C32 [n_tiles * 128, N] fp32.  No host
+ * knowledge of the segment sizes is needed: the table is built on the device. */
+int b200_gemm_wt_f32_grouped(const void* X, long ldx, const void* W, long ldw, float* C32, long ldc32,
+                             const int* tile_group, int n_tiles, int n_groups, int N, int K_w, void* stream) {
+  B200_REQUIRE(X && W && C32 && tile_group && n_tiles > 0 && n_groups > 0, "gemm_wt_f32_grouped: bad argument");
+  const int kbw = cdiv(K_w, 64);
+  WtExt ext;
+  ext.kb_w = kbw; ext.k_w = K_w; ext.ldw = ldw; ext.C32 = C32; ext.res32 = nullptr; ext.ldc32 = ldc32; ext.ldr32 = 0;
+  ext.Csplit = nullptr; ext.ld_split = 0; ext.n_pad = 0; ext.tile_group = tile_group; ext.n_groups = n_groups;
+  // token tile 128 (the padding unit of the segments), one k-block per stage, three stages: two CTAs per SM
+  const WtConfig cfg{128, 1, 3, 1};
+  return gemm_wt(X, ldx, W, nullptr, nullptr, 0, nullptr, 0, nullptr, n_tiles * 128, N, kbw * 64, B200_EPI_NONE,
+                 B200_WT_F32, 0, cfg, 0, (cudaStream_t)stream, &ext);
+}
 /* Many independent small Linears of one shape family in ONE call (the experts of a mixture over their token segments,
  * the heads of a per-head projection): product i is  C32 + c_off[i] [rows[i], N] = (X + x_off[i]) [rows[i], ceil64(K_w)]
  * . (W + w_off[i]) [N, K_w]^T, offsets in elements, launched round-robin on `streams` so that they overlap (each fills

@@ -208,30 +208,23 @@ class ExpertMixture:
 
 
     def _experts_prompt(self, ops: LayerOps, x, lists, count):
-        """A prompt step on the tensor cores.  The (token, choice) entries are sorted by expert; ONE launch gathers
-        and rounds all input rows in that order, every expert with tokens runs two tcgen05 products over its
-        contiguous segment (the host reads the experts' token counts: one small copy per layer), ONE launch applies
-        relu^2 and rounds the hidden rows, ONE launch scatters the outputs back to entry order."""
+        """A prompt step on the tensor cores, without the host knowing how the tokens spread over the experts: the
+        (token, choice) entries are sorted by expert into segments padded to whole token tiles, with the expert of
+        every tile in a device table; ONE launch gathers and rounds all input rows in that order, ONE grouped tcgen05
+        launch per projection multiplies every tile by its expert's weights (empty tiles leave at once), ONE launch
+        applies relu^2 and rounds the hidden rows, ONE launch scatters the outputs back to entry order."""
         w, T = self.w, x.shape[0]
         n_all = T * self.top
-        order = ops.moe_order(lists, count)
-        with torch.cuda.stream(ops.stream):
-            counts = count.to("cpu").tolist()
-        xs = ops.to_bf16(x, self.W, rows=n_all, row_map=order, div=self.top)
-        hs = ops.empty((n_all, self.ff))
-        seg, at = [], 0
-        for e, n in enumerate(counts):
-            if n:
-                seg.append((e, at, n))
-            at += n
-        ops.tc_gemm_many(xs, w["up"], hs, [(a * xs.stride(0), e * self.ff * self.W, a * self.ff, n) for e, a, n in seg],
-                         N_=self.ff, K=self.W, ldw=self.W)
+        order, group = ops.moe_tiles(lists, count, n_all)
+        n_rows = order.shape[0]
+        xs = ops.to_bf16(x, self.W, rows=n_rows, row_map=order, div=self.top)
+        hs = ops.empty((n_rows, self.ff))
+        ops.tc_gemm_grouped(xs, w["up"], hs, group, N_=self.ff, K=self.W, n_groups=self.E)
         hb = ops.to_bf16(hs, self.ff, relu2=True)
-        ys = ops.empty((n_all, self.W))
-        ops.tc_gemm_many(hb, w["down"], ys, [(a * hb.stride(0), e * self.W * self.ff, a * self.W, n) for e, a, n in seg],
-                         N_=self.W, K=self.ff, ldw=self.ff)
+        ys = ops.empty((n_rows, self.W))
+        ops.tc_gemm_grouped(hb, w["down"], ys, group, N_=self.W, K=self.ff, n_groups=self.E)
         out = ops.empty((n_all, self.W))
-        ops.rows_scatter(ys, order, out, n_all)
+        ops.rows_scatter(ys, order, out, n_rows)
         return out
 
 

@@ -241,6 +241,23 @@ class LayerOps:
             e.record(s)
             main.wait_event(e)
 
+    def moe_tiles(self, lists: torch.Tensor, count: torch.Tensor, n_entries: int, tile: int = 128):
+        """-> (order (n_rows,), tile_group (n_rows / tile,)): the entries sorted by expert in segments padded to whole
+        tiles; n_rows bounds any distribution of the entries over the experts"""
+        E = lists.shape[0]
+        n_rows = (n_entries + E * (tile - 1) + tile - 1) // tile * tile
+        order, group = self.empty((n_rows,), torch.int32), self.empty((n_rows // tile,), torch.int32)
+        self._ok(self.lib.b200_lm_moe_tiles(lists.data_ptr(), lists.stride(0), count.data_ptr(), E, tile,
+                                            order.data_ptr(), n_rows, group.data_ptr(), self.s), "lm_moe_tiles")
+        return order, group
+
+    def tc_gemm_grouped(self, Xb: torch.Tensor, W: torch.Tensor, Y: torch.Tensor, tile_group: torch.Tensor, *, N_: int,
+                        K: int, n_groups: int):
+        """Y[tile y] = Xb[tile y] . W[tile_group[y]]^T for every token tile of 128 rows, ONE tcgen05 launch"""
+        self._ok(self.lib.b200_gemm_wt_f32_grouped(Xb.data_ptr(), Xb.stride(0), W.data_ptr(), K, Y.data_ptr(),
+                                                   Y.stride(0), tile_group.data_ptr(), tile_group.shape[0], n_groups,
+                                                   N_, K, self.s), "gemm_wt_f32_grouped")
+
     def rows_scatter(self, X: torch.Tensor, dst_map: torch.Tensor, out: torch.Tensor, rows: int):
         self._ok(self.lib.b200_lm_rows_scatter(X.data_ptr(), X.stride(0), dst_map.data_ptr(), out.data_ptr(),
                                                out.stride(0), rows, X.shape[1], self.s), "lm_rows_scatter")
