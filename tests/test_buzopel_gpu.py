@@ -201,6 +201,34 @@ def test_row_gemm_both_kernels(M, N, K, batch):
     assert (host(eng, Y) - want).abs().max() < 1e-4
 
 
+def test_grouped_tensor_core_gemm_over_padded_segments():
+    """entries sorted by expert into segments padded to whole tiles; an expert with several tiles, one with a partial
+    tile, one with none; every row against a plain product with its own expert's weights"""
+    from mlx_vlm_b200.layer_engine import LayerEngine
+    if "eng16" not in _MODELS:
+        _MODELS["eng16"] = LayerEngine("cuda:0", exact=False)
+    eng = _MODELS["eng16"]
+    ops = eng.ops
+    E, K, N_, top = 4, 72, 40, 1
+    g = torch.Generator().manual_seed(8)
+    counts = [300, 0, 130, 5]
+    idx = torch.cat([torch.full((c,), e) for e, c in enumerate(counts)])[torch.randperm(sum(counts), generator=g)]
+    T = idx.shape[0]
+    x = torch.randn(T, K, generator=g)
+    W = (torch.randn(E, N_, K, generator=g) / 8).bfloat16()
+    lists, count = ops.moe_group(dev(idx.view(T, 1), torch.int32), E)
+    order, group = ops.moe_tiles(lists, count, T)
+    xs = ops.to_bf16(dev(x), K, rows=order.shape[0], row_map=order, div=top)
+    ys = ops.empty((order.shape[0], N_))
+    ops.tc_gemm_grouped(xs, dev(W, torch.bfloat16), ys, group, N_=N_, K=K, n_groups=E)
+    out = ops.empty((T, N_))
+    ops.rows_scatter(ys, order, out, order.shape[0])
+    eng.stream.synchronize()
+    assert group.cpu().tolist()[:6] == [0, 0, 0, 2, 2, 3] and set(group.cpu().tolist()[6:]) <= {-1}
+    want = torch.einsum("tk,tnk->tn", x.bfloat16().double(), W.double()[idx])
+    assert (host(eng, out) - want).abs().max() < 2e-3
+
+
 def _attend(eng, cache, q, slot, pos, H, r, scale):
     out = dev(torch.zeros(q.shape[0], H * r))
     eng.ops.latent_attention(dev(q), cache, dev(slot, torch.int32), dev(pos, torch.int32), out, H, r, scale)
