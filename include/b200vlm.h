@@ -325,12 +325,10 @@ int b200_gemm_wt_f32(const void* X, long ldx, const void* W, long ldw, const voi
  * rows lie in segments padded to whole tiles (b200_lm_moe_tiles builds the table on the device) */
 int b200_gemm_wt_f32_grouped(const void* X, long ldx, const void* W, long ldw, float* C32, long ldc32,
                              const int* tile_group, int n_tiles, int n_groups, int N, int K_w, void* stream);
-/* many independent small Linears of one shape family in one call (a mixture's experts over their token segments, the
- * heads of a per-head projection): product i is C32 + c_off[i] [rows[i], N] = (X + x_off[i]) . (W + w_off[i])^T, one
- * bf16 part, offsets in elements, launched round-robin on `streams` (ordered by the caller's events) */
-int b200_gemm_wt_f32_many(const void* X, long ldx, const void* W, long ldw, float* C32, long ldc32, const long* x_off,
-                          const long* w_off, const long* c_off, const int* rows, int n, int N, int K_w,
-                          void* const* streams, int n_streams);
+/* the per-head projections of one token set in ONE launch: head g multiplies columns [g * x_group_cols, + K_w) of
+ * X [T, x_cols] (bf16; K_w % 64 == 0) by W[g] [N, K_w] and writes columns [g * c_group_cols, + N) of C32 */
+int b200_gemm_wt_f32_heads(const void* X, long ldx, int x_cols, int x_group_cols, const void* W, long ldw, float* C32,
+                           long ldc32, long c_group_cols, int T, int n_heads, int N, int K_w, void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Lock-step batched decode (continuous batching; generate/ar.py:929-1390        */

@@ -123,8 +123,8 @@ LM_SIGNATURES = {
                                _I, _I, _P]),
     "b200_lm_argmax_rows": (_I, [_P, _L, _I, _P, _P, _I, _P]),
     "b200_lm_rows_to_bf16": (_I, [_P, _L, _P, _I, _P, _L, _I, _I, _I, _I, _P]),
-    "b200_gemm_wt_f32_many": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _P, _I]),
     "b200_gemm_wt_f32_grouped": (_I, [_P, _L, _P, _L, _P, _L, _P, _I, _I, _I, _I, _P]),
+    "b200_gemm_wt_f32_heads": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _L, _I, _I, _I, _I, _P]),
     "b200_lm_moe_tiles": (_I, [_P, _L, _P, _I, _I, _P, _I, _P, _P]),
     "b200_lm_moe_order": (_I, [_P, _L, _P, _I, _P, _P]),
     "b200_lm_rows_scatter": (_I, [_P, _L, _P, _P, _L, _I, _I, _P]),

@@ -196,6 +196,12 @@ struct WtExt {
   // n_groups x N rows.  Launched plainly (no programmatic dependent launch): the table is read at the top of the kernel.
   const int* tile_group = nullptr;
   int n_groups = 0;
+  // column groups (the heads of a per-head projection over the SAME tokens): group g multiplies columns
+  // [g * x_group_cols, + K) of X by the weight rows of group g and writes columns [g * c_group_cols, + N) of C32;
+  // W holds col_groups x N rows, X has x_cols columns in all.  One launch, grid.y = col_groups x token tiles.
+  int col_groups = 0;
+  int x_group_cols = 0, x_cols = 0;
+  long c_group_cols = 0;
 };
 void gemm_wt_auto(int T, int row_blocks, int K, bool allow_split, WtConfig* c, int sm_count);
 int gemm_wt(const void* X, long ldx, const void* W, const void* bias, const void* residual, long ldr,

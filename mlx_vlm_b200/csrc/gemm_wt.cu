@@ -66,6 +66,8 @@ struct WtParams {
   long ld_split;
   int n_pad;
   const int* tile_group;  // grouped products: token tile y multiplies the weight rows of group tile_group[y] (< 0: empty)
+  int col_groups, x_group_cols;  // column groups: blockIdx.y = group x token tile; X columns / C32 columns move with the group
+  long c_group_cols;
 };
 
 __device__ __forceinline__ uint32_t w_smem_u32(const void* p) {
@@ -192,13 +194,21 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const bool swiglu = !TOWER && (p.mode == B200_WT_SWIGLU);
   const int rb = blockIdx.x;
   const int n0 = rb * (swiglu ? 64 : WT_ROWS);  // first output feature (SwiGLU: channel) of the tile
-  const int t0 = blockIdx.y * p.TN;
   int n0w = n0;                                 // first weight row of the tile (grouped: inside the tile's group)
+  int ty = blockIdx.y, xk0 = 0;                 // token tile; first X column (column groups)
+  long cg = 0;                                  // first C32 column (column groups)
   if (p.tile_group) {
     const int g = p.tile_group[blockIdx.y];
     if (g < 0) return;                          // an empty token tile: nothing is allocated yet
     n0w += g * p.N;
+  } else if (p.col_groups > 0) {
+    const int tpg = gridDim.y / p.col_groups, g = ty / tpg;
+    ty -= g * tpg;
+    n0w += g * p.N;
+    xk0 = g * p.x_group_cols;
+    cg = (long)g * p.c_group_cols;
   }
+  const int t0 = ty * p.TN;
   const int split = blockIdx.z;
   const int kb_total = (p.K + WT_BK - 1) / WT_BK;
   const int kb0 = split * p.kb_per_split;
@@ -237,7 +247,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     uint8_t* sX = ring + (long)s * stage_bytes + p.KS * WT_WBLK;
     const int cnt = min(p.KS, kb1 - kb0 - it * p.KS);
     for (int j = 0; j < cnt; ++j)
-      w_tma_2d(sX + j * xblk, &tmX, &full_bar[s], (kb0 + it * p.KS + j) * WT_BK, t0);
+      w_tma_2d(sX + j * xblk, &tmX, &full_bar[s], (kb0 + it * p.KS + j) * WT_BK + xk0, t0);
   };
 
   const int pre = n_it < NS ? n_it : NS;
@@ -400,8 +410,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           if (c0 + tl >= p.TN || t >= p.T || n >= p.N) continue;
           float4 v = *reinterpret_cast<const float4*>(stg + (tl * WT_ROWS + ch * 4) * 4);
           if (p.mode == B200_WT_F32) {
-            float* dst = p.C32 + (long)t * p.ldc32 + n;
-            if (n + 4 <= p.N && (p.ldc32 & 3) == 0) {
+            float* dst = p.C32 + (long)t * p.ldc32 + cg + n;
+            if (n + 4 <= p.N && (p.ldc32 & 3) == 0 && (cg & 3) == 0) {
               if (p.res32) {
                 const float4 r = *reinterpret_cast<const float4*>(p.res32 + (long)t * p.ldr32 + n);
                 v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
@@ -797,7 +807,12 @@ int gemm_wt(const void* X, long ldx, const void* W, const void* bias, const void
     p.Csplit = ext->Csplit; p.ld_split = ext->ld_split; p.n_pad = ext->n_pad;
     if (ext->kb_w > 0) k_w = ext->k_w;
     p.tile_group = ext->tile_group;
+    p.col_groups = ext->col_groups; p.x_group_cols = ext->x_group_cols; p.c_group_cols = ext->c_group_cols;
   }
+  const bool heads = ext && ext->col_groups > 0;
+  B200_REQUIRE(!heads || (mode == B200_WT_F32 && cfg.split == 1 && !bias && !ext->res32 && !ext->tile_group &&
+                          ext->x_group_cols % 8 == 0 && ext->x_cols >= (ext->col_groups - 1) * ext->x_group_cols + k_w),
+               "gemm_wt: column groups are fp32-output, unsplit, without bias / residual, 16-byte column offsets");
   const bool grouped = ext && ext->tile_group;
   B200_REQUIRE(!grouped || (mode == B200_WT_F32 && ext->n_groups > 0 && cfg.split == 1 && !bias),
                "gemm_wt: grouped products are fp32-output, unsplit, without bias");
@@ -806,10 +821,11 @@ int gemm_wt(const void* X, long ldx, const void* W, const void* bias, const void
   B200_REQUIRE(smem <= 227 * 1024 - 1024, "gemm_wt: %zu B of shared memory", smem);
   B200_REQUIRE((size_t)cfg.stages * stage >= (size_t)WT_EPI_TOK * WT_ROWS * 4, "gemm_wt: ring smaller than the epilogue staging tile");
   CUtensorMap tw, tx;
-  int rc = wt_tmap(W, (long)(ext && ext->ldw > 0 ? ext->ldw : k_w), grouped ? ext->n_groups * N : N, k_w,
+  int rc = wt_tmap(W, (long)(ext && ext->ldw > 0 ? ext->ldw : k_w),
+                   grouped ? ext->n_groups * N : (heads ? ext->col_groups * N : N), k_w,
                    mode == B200_WT_SWIGLU ? 64 : WT_ROWS, &tw);
   if (rc) return rc;
-  if ((rc = wt_tmap(X, ldx, T, K, cfg.TN, &tx))) return rc;
+  if ((rc = wt_tmap(X, ldx, T, heads ? ext->x_cols : K, cfg.TN, &tx))) return rc;
   static unsigned long long set_mask = 0ull;
   int dev = 0;
   B200_CUDA(cudaGetDevice(&dev));
@@ -824,7 +840,7 @@ int gemm_wt(const void* X, long ldx, const void* W, const void* bias, const void
   }
   const int row_blocks = mode == B200_WT_SWIGLU ? cdiv(inter, 64) : cdiv(N, WT_ROWS);
   cudaLaunchConfig_t lc = {};
-  lc.gridDim = dim3(row_blocks, cdiv(T, cfg.TN), splits);
+  lc.gridDim = dim3(row_blocks, cdiv(T, cfg.TN) * (heads ? ext->col_groups : 1), splits);
   lc.blockDim = dim3(256);
   lc.dynamicSmemBytes = smem;
   lc.stream = st;

@@ -665,27 +665,16 @@ int b200_gemm_wt_f32_grouped(const void* X, long ldx, const void* W, long ldw, f
   return gemm_wt(X, ldx, W, nullptr, nullptr, 0, nullptr, 0, nullptr, n_tiles * 128, N, kbw * 64, B200_EPI_NONE,
                  B200_WT_F32, 0, cfg, 0, (cudaStream_t)stream, &ext);
 }
-/* Many independent small Linears of one shape family in ONE call (the experts of a mixture over their token segments,
- * the heads of a per-head projection): product i is  C32 + c_off[i] [rows[i], N] = (X + x_off[i]) [rows[i], ceil64(K_w)]
- * . (W + w_off[i]) [N, K_w]^T, offsets in elements, launched round-robin on `streams` so that they overlap (each fills
- * a fraction of the SMs).  The caller orders the streams before and after (events). */
-int b200_gemm_wt_f32_many(const void* X, long ldx, const void* W, long ldw, float* C32, long ldc32, const long* x_off,
-                          const long* w_off, const long* c_off, const int* rows, int n, int N, int K_w,
-                          void* const* streams, int n_streams) {
-  B200_REQUIRE(X && W && C32 && x_off && w_off && c_off && rows && streams && n_streams > 0, "gemm_wt_f32_many: bad argument");
-  const int kbw = cdiv(K_w, 64);
-  int launched = 0;
-  for (int i = 0; i < n; ++i) {
-    if (rows[i] <= 0) continue;
-    WtExt ext;
-    ext.kb_w = kbw; ext.k_w = K_w; ext.ldw = ldw; ext.C32 = C32 + c_off[i]; ext.res32 = nullptr; ext.ldc32 = ldc32;
-    ext.ldr32 = 0; ext.Csplit = nullptr; ext.ld_split = 0; ext.n_pad = 0;
-    const int rc = gemm_wt_tuned((const bf16*)X + x_off[i], ldx, (const bf16*)W + w_off[i], nullptr, nullptr, 0, nullptr, 0,
-                                 nullptr, 0, rows[i], N, kbw * 64, B200_EPI_NONE, B200_WT_F32, 0, false, 148, nullptr,
-                                 (cudaStream_t)streams[launched % n_streams], &ext);
-    if (rc != B200_OK) return rc;
-    ++launched;
-  }
-  return B200_OK;
+/* The per-head projections of ONE token set in ONE launch: head g multiplies columns [g * x_group_cols, + K_w) of
+ * X [T, x_cols] (bf16, K_w a multiple of 64) by W[g] [N, K_w] and writes columns [g * c_group_cols, + N) of C32 [T, ..]. */
+int b200_gemm_wt_f32_heads(const void* X, long ldx, int x_cols, int x_group_cols, const void* W, long ldw, float* C32,
+                           long ldc32, long c_group_cols, int T, int n_heads, int N, int K_w, void* stream) {
+  B200_REQUIRE(X && W && C32 && n_heads > 0 && K_w % 64 == 0, "gemm_wt_f32_heads: bad argument (K must be whole k-blocks)");
+  WtExt ext;
+  ext.kb_w = K_w / 64; ext.k_w = K_w; ext.ldw = ldw; ext.C32 = C32; ext.res32 = nullptr; ext.ldc32 = ldc32; ext.ldr32 = 0;
+  ext.Csplit = nullptr; ext.ld_split = 0; ext.n_pad = 0;
+  ext.col_groups = n_heads; ext.x_group_cols = x_group_cols; ext.x_cols = x_cols; ext.c_group_cols = c_group_cols;
+  return gemm_wt_tuned(X, ldx, W, nullptr, nullptr, 0, nullptr, 0, nullptr, 0, T, N, K_w, B200_EPI_NONE, B200_WT_F32, 0,
+                       false, 148, nullptr, (cudaStream_t)stream, &ext);
 }
 }

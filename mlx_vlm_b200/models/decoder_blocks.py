@@ -103,11 +103,11 @@ class LatentAttention:
         q = ops.linear(cq, w["uq"])
         qa = ops.empty((T, H * Dl))
         heads_tc = ops.tc_ok(T, dn, dn + dr, r) and dn % 64 == 0 and r % 64 == 0 and Dl % 4 == 0 and dv % 4 == 0
-        if heads_tc:     # a prompt: one tcgen05 product per head, overlapped (inner sizes are whole k-blocks)
+        if heads_tc:     # a prompt: the heads' products as ONE tcgen05 launch (inner sizes are whole k-blocks)
             try:
                 qb = ops.to_bf16(q, H * (dn + dr))
-                ops.tc_gemm_many(qb, w["ukT"], qa, [(h * (dn + dr), h * r * dn, h * Dl, T) for h in range(H)], N_=r, K=dn,
-                                 ldw=dn)
+                ops.tc_gemm_heads(qb, w["ukT"], qa, H=H, N_=r, K=dn, x_cols=qb.shape[1], x_group_cols=dn + dr,
+                                  c_group_cols=Dl)
             except _B200Error as e:
                 ops.tc_refused(e)
                 heads_tc = False
@@ -134,7 +134,7 @@ class LatentAttention:
         if heads_tc:
             try:
                 ob = ops.to_bf16(ol, H * r)
-                ops.tc_gemm_many(ob, w["uv"], att, [(h * r, h * dv * r, h * dv, T) for h in range(H)], N_=dv, K=r, ldw=r)
+                ops.tc_gemm_heads(ob, w["uv"], att, H=H, N_=dv, K=r, x_cols=ob.shape[1], x_group_cols=r, c_group_cols=dv)
             except _B200Error as e:
                 ops.tc_refused(e)
                 heads_tc = False

@@ -32,8 +32,6 @@ class LayerOps:
         self._inv_freq = {}
         self._on_stream = False
         self.tc_enabled = True
-        self._side = None             # side streams for many small independent products (experts, heads)
-        self._tuned = set()           # product classes whose configuration the GEMM has already measured
 
     @property
     def s(self) -> int:
@@ -199,48 +197,6 @@ class LayerOps:
                                             self.s), "lm_moe_order")
         return order
 
-    def tc_gemm_many(self, X: torch.Tensor, W: torch.Tensor, Y: torch.Tensor, jobs, *, N_: int, K: int, ldw: int,
-                     n_streams: int = 4):
-        """Independent small products of one shape family (an expert's or a head's) in ONE native call, spread over
-        side streams so that they overlap (each fills a fraction of the SMs).  jobs: (x_off, w_off, y_off, rows) in
-        elements of X (bf16, row pitch X.stride(0)), W (bf16, row pitch ldw) and Y (fp32, row pitch Y.stride(0)).
-        The operands were produced on the engine's stream and stay referenced by the caller until the streams have
-        joined.  The first product of a size class runs alone on the engine's stream: the GEMM measures its
-        configuration on first use."""
-        if self._side is None:
-            self._side = [torch.cuda.Stream(device=self.device) for _ in range(n_streams)]
-        later = []
-        for xo, wo, yo, rows in jobs:
-            if rows <= 0:
-                continue
-            key = (rows // 64, N_, K)
-            if key in self._tuned:
-                later.append((xo, wo, yo, rows))
-                continue
-            self._tuned.add(key)
-            self._ok(self.lib.b200_gemm_wt_f32(X.data_ptr() + 2 * xo, X.stride(0), W.data_ptr() + 2 * wo, ldw, 0, 0, 0,
-                                               Y.data_ptr() + 4 * yo, Y.stride(0), 0, 0, 0, rows, N_, K, 1, 0, WT_F32,
-                                               self.s), "gemm_wt_f32")
-        if not later:
-            return
-        main = self.stream
-        fork = torch.cuda.Event()
-        fork.record(main)
-        for s in self._side:
-            s.wait_event(fork)
-        arr = np.asarray(later, dtype=np.int64)
-        xo, wo, yo = (np.ascontiguousarray(arr[:, i]) for i in range(3))
-        rows = np.ascontiguousarray(arr[:, 3], dtype=np.int32)
-        streams = (N.C.c_void_p * len(self._side))(*[s.cuda_stream for s in self._side])
-        self._ok(self.lib.b200_gemm_wt_f32_many(X.data_ptr(), X.stride(0), W.data_ptr(), ldw, Y.data_ptr(), Y.stride(0),
-                                                xo.ctypes.data, wo.ctypes.data, yo.ctypes.data, rows.ctypes.data,
-                                                len(later), N_, K, streams, len(self._side)), "gemm_wt_f32_many")
-        self.launches += len(later) - 1
-        for s in self._side:
-            e = torch.cuda.Event()
-            e.record(s)
-            main.wait_event(e)
-
     def moe_tiles(self, lists: torch.Tensor, count: torch.Tensor, n_entries: int, tile: int = 128):
         """-> (order (n_rows,), tile_group (n_rows / tile,)): the entries sorted by expert in segments padded to whole
         tiles; n_rows bounds any distribution of the entries over the experts"""
@@ -257,6 +213,13 @@ class LayerOps:
         self._ok(self.lib.b200_gemm_wt_f32_grouped(Xb.data_ptr(), Xb.stride(0), W.data_ptr(), K, Y.data_ptr(),
                                                    Y.stride(0), tile_group.data_ptr(), tile_group.shape[0], n_groups,
                                                    N_, K, self.s), "gemm_wt_f32_grouped")
+
+    def tc_gemm_heads(self, Xb: torch.Tensor, W: torch.Tensor, Y: torch.Tensor, *, H: int, N_: int, K: int,
+                      x_cols: int, x_group_cols: int, c_group_cols: int):
+        """Y[:, g * c_group_cols : + N_] = Xb[:, g * x_group_cols : + K] . W[g]^T for every head g, ONE tcgen05 launch"""
+        self._ok(self.lib.b200_gemm_wt_f32_heads(Xb.data_ptr(), Xb.stride(0), x_cols, x_group_cols, W.data_ptr(), K,
+                                                 Y.data_ptr(), Y.stride(0), c_group_cols, Xb.shape[0], H, N_, K, self.s),
+                 "gemm_wt_f32_heads")
 
     def rows_scatter(self, X: torch.Tensor, dst_map: torch.Tensor, out: torch.Tensor, rows: int):
         self._ok(self.lib.b200_lm_rows_scatter(X.data_ptr(), X.stride(0), dst_map.data_ptr(), out.data_ptr(),
