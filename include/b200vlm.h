@@ -435,6 +435,43 @@ int b200_lm_argmax_rows(const float* z, long ldz, int V, int* tok, float* logpro
 int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* active, int* log, int log_stride,
                          int log_rows, int* step, const float* lp, float* lp_log, int B, void* stream);
 
+/* ------------------------------------------------------------------------- */
+/* Sequence mixers (csrc/mixer_ops.cu).  A step's tokens are its sequences'    */
+/* tokens one after the other: first[t] = row of the first token of t's        */
+/* sequence, seqs[g] = (first row, rows).  State buffers are fp32 per slot.    */
+/* ------------------------------------------------------------------------- */
+/* Y[t][c] = act(sum_j w[c][j] U[t - (taps-1) + j][c]); inputs before the step come from state[slot] = the
+ * taps-1 inputs before the step's first token ([taps-1][C]), zeros before position 0; the state is then advanced */
+int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
+                       const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
+                       int act, int T, void* stream);
+/* rotate-half rotary (first rot_dims of every head) on Q in place and on K; cache[slot[t]][pos[t]] = [K | V] */
+int b200_lm_qkv_post(float* Q, long ldq, const float* K, long ldk, const float* V, long ldv, void* cache, int cache_bf16,
+                     long slot_stride, long tok_stride, const int* slot, const int* pos, const float* cs, int H, int G,
+                     int dim, int vdim, int rot_dims, int T, void* stream);
+/* out[t][h] = softmax over the visible rows j of slot[t] (and the sink logit of head h, if any) of
+ * scale * q[t][h] . K_j[h / (H/G)], times V_j; visible: max(block start of pos[t] (chunk > 0), pos[t] - window + 1
+ * (window > 0), 0) <= j <= pos[t].  n_split > 1: key tiles dealt to n_split blocks, part [T][H][n_split][vdim + 2] */
+int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cache_bf16, long slot_stride, long tok_stride,
+                           const int* slot, const int* pos, float* out, long ldo, const void* sink, int H, int G,
+                           int dim, int vdim, float scale, int chunk, int window, float* part, int n_split, int T,
+                           void* stream);
+/* per head a (dim, vdim) state carried through each sequence: S <- decay S + k u^T, out = S^T q, u = v or
+ * (delta) beta (v - (decay S)^T k); decay per head (decay_const) or exp(-exp(A_log) softplus(a + dt_bias)) per
+ * token; beta = sigmoid(b) or 1; q, k shared by `rep` heads, optionally silu'd (act) and scaled to unit length */
+int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv, float* out, long ldo,
+                         float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
+                         int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
+                         const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
+                         const float* b, long ldb, int delta, void* stream);
+/* out[t][c] = scale * o[t][c] * [rsqrt(mean over c's group of `span` + eps)] * [w[c mod w_len]] * [act(gate)] */
+int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, const void* w, int w_len, float eps, int span,
+                      int gate_per_head, int gate_silu, int dv, int n, float scale, float* out, long ldo, int T,
+                      void* stream);
+/* Y = g sigmoid(alpha g) (u + 1), g = min(G, limit), u = clamp(U, -limit, limit) */
+int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float* Y, long ldy,
+                      int n, int T, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

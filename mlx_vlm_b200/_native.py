@@ -132,6 +132,15 @@ LM_SIGNATURES = {
     "b200_lm_cache_transpose": (_I, [_P, _L, _I, _I, _I, _P, _P]),
     "b200_gemm_wt_f32": (_I, [_P, _L, _P, _L, _P, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P]),
     "b200_lm_advance_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _P]),
+    # csrc/mixer_ops.cu
+    "b200_lm_short_conv": (_I, [_P, _L, _P, _P, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "b200_lm_qkv_post": (_I, [_P, _L, _P, _L, _P, _L, _P, _I, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "b200_lm_sink_attention": (_I, [_P, _L, _P, _I, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _P, _I, _I,
+                                    _P]),
+    "b200_lm_linear_state": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F,
+                                  _P, _P, _L, _P, _P, _P, _L, _I, _P]),
+    "b200_lm_head_post": (_I, [_P, _L, _P, _L, _P, _I, _F, _I, _I, _I, _I, _I, _F, _P, _L, _I, _P]),
+    "b200_lm_glu_clamp": (_I, [_P, _L, _P, _L, _F, _F, _P, _L, _I, _I, _P]),
 }
 SIGNATURES.update(LM_SIGNATURES)
 

@@ -4,7 +4,7 @@
 it travels with the repo snapshot to the GPU box (it is git-ignored).  Targets:
   b200vlm   the whole C ABI (every model family)
   b200lm    the layer-level ops alone (decoder designs assembled layer by layer on the host): with the
-            tcgen05 GEMM they feed: a fresh checkout that only serves such a model compiles four files
+            tcgen05 GEMM they feed: a fresh checkout that only serves such a model compiles five files
 """
 from __future__ import annotations
 
@@ -16,7 +16,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200vlm.so")
-LM_SOURCES = ["errors.cu", "layer_ops.cu", "gemm_wt.cu", "tower_f32.cu"]
+LM_SOURCES = ["errors.cu", "layer_ops.cu", "mixer_ops.cu", "gemm_wt.cu", "tower_f32.cu"]
 SOURCES = LM_SOURCES + ["engine.cu", "gemm_tcgen05.cu", "rowops.cu", "attention.cu", "decode.cu", "decode_mega.cu",
            "decode_mega_tc.cu", "attention_tc.cu", "attention_fa.cu", "decode_batch.cu"]
 NVCC_FLAGS = [

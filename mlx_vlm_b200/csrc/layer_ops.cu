@@ -391,7 +391,7 @@ struct GemmRowsP {
   const int* count;                      // per batch: rows (device); NULL: M rows, no list
   int x_div;
   int M, N, K;
-  int epi; float epi_param;              // 0 none, 1 relu^2, 2 param * tanh(v / param)
+  int epi; float epi_param;              // 0 none, 1 relu^2, 2 param * tanh(v / param), 3 added to the output
   int round_x;
   int compact, n_batch;                  // compact: blockIdx.z counts the batches that HAVE rows (count[b] > 0) —
 };                                       // a decode step launches top x rows slices, not one per expert
@@ -421,6 +421,10 @@ __device__ __forceinline__ float gemm_epi(float v, int epi, float param) {
   if (epi == 1) { v = fmaxf(v, 0.f); return v * v; }
   if (epi == 2) return param * tanhf(v / param);
   return v;
+}
+// epi 3: the product is added to what the output row holds (a residual stream that accumulates in place)
+__device__ __forceinline__ void gemm_store(float* y, float v, int epi, float param) {
+  *y = epi == 3 ? *y + v : gemm_epi(v, epi, param);
 }
 constexpr int GB_M = 64, GB_N = 64, GB_K = 16;
 __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmRowsP p) {
@@ -491,7 +495,7 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmRowsP p) {
       if (n >= p.N) continue;
       float v = acc[i][j];
       if (p.bias) v += bf2f(p.bias[n]);
-      Y[(long)yr * p.ldy + n] = gemm_epi(v, p.epi, p.epi_param);
+      gemm_store(&Y[(long)yr * p.ldy + n], v, p.epi, p.epi_param);
     }
   }
 }
@@ -534,7 +538,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmRowsP p) {
 #pragma unroll
     for (int i = 0; i < GS_R; ++i) {
       const float v = warp_sum(acc[i]);
-      if (lane == 0 && yr[i] >= 0) Y[(long)yr[i] * p.ldy + n] = gemm_epi(v + bias, p.epi, p.epi_param);
+      if (lane == 0 && yr[i] >= 0) gemm_store(&Y[(long)yr[i] * p.ldy + n], v + bias, p.epi, p.epi_param);
     }
   }
 }
@@ -616,7 +620,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemm_skinny_vec_kernel(GemmRows
 #pragma unroll
     for (int i = 0; i < MR; ++i) {
       const float v = warp_sum(acc[r][i]);
-      if (lane == 0 && n < p.N && yrow[i] >= 0) Y[(long)yrow[i] * p.ldy + n] = gemm_epi(v + bias, p.epi, p.epi_param);
+      if (lane == 0 && n < p.N && yrow[i] >= 0) gemm_store(&Y[(long)yrow[i] * p.ldy + n], v + bias, p.epi, p.epi_param);
     }
   }
 }
@@ -790,7 +794,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_blk_kernel(GemmRowsP p) {
     for (int w = 0; w < 8; ++w) v += red[w][r][i];
     if (n < p.N && yrow[i] >= 0) {
       if (p.bias) v += bf2f(p.bias[n]);
-      (p.Y + (long)b * p.yb)[(long)yrow[i] * p.ldy + n] = gemm_epi(v, p.epi, p.epi_param);
+      gemm_store(&(p.Y + (long)b * p.yb)[(long)yrow[i] * p.ldy + n], v, p.epi, p.epi_param);
     }
   }
 }

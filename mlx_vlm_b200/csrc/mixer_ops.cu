@@ -1,0 +1,542 @@
+// Sequence mixers beside the latent attention of layer_ops.cu, for decoder designs assembled on the host
+// (models/decoder_blocks.py).  Every token of a step names its cache slot and its position; a step's tokens are
+// the concatenation of its sequences' tokens, `first[t]` is the row of the first token of t's sequence in the step
+// and `seqs[g] = (first row, rows)` lists the sequences.  A prompt, a portion of one, a decoded token and a batch of
+// unequal requests are therefore the same launches.
+//   * short causal convolution over time per channel, the last taps - 1 inputs of a sequence kept per slot,
+//   * rotate-half rotary on queries and keys + the write of the key / value rows of the step into the cache,
+//   * softmax attention over cached rows [keys of all kv heads | values of all kv heads] with grouped query heads,
+//     an optional block-local or sliding range of visible keys and an optional sink logit per head that joins the
+//     denominator without a key or a value,
+//   * a per-head matrix state carried from token to token, S <- decay S + k u^T, o = S^T q, with u = v (decayed
+//     outer-product memory) or u = beta (v - S^T k) (gated delta rule), the state in fp32 per slot,
+//   * per-head / per-token output norms and gates, and a clamped gated feed-forward activation.
+// All arithmetic is fp32; cache rows are bf16 in the serving mode and fp32 in the exact mode.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+__device__ __forceinline__ float ld_row(const float* p) { return *p; }
+__device__ __forceinline__ float ld_row(const bf16* p) { return bf2f(*p); }
+__device__ __forceinline__ void st_row(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st_row(bf16* p, float v) { *p = f2bf(v); }
+__device__ __forceinline__ float sigmoid_exact(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_exact(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_exact(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------------------------------------------------
+// short convolution: y[t][c] = act( sum_j w[c][j] * u[t - (taps - 1) + j][c] ), inputs before the step come from
+// the slot's state (the taps - 1 inputs that precede the step's first token), inputs before position 0 are zero
+struct ConvP {
+  const float* U; long ldu;
+  const bf16* w;                   // [C][taps]
+  float* Y; long ldy;
+  float* state; long slot_stride;  // per slot [taps - 1][C]
+  const int *slot, *pos, *first;
+  int C, taps, act;
+};
+__global__ void short_conv_kernel(ConvP p) {
+  const int t = blockIdx.x;
+  const int back = t - p.first[t], ps = p.pos[t];
+  const float* st = p.state + (long)p.slot[t] * p.slot_stride;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.C; c += blockDim.x * gridDim.y) {
+    float a = 0.f;
+    for (int j = 0; j < p.taps; ++j) {
+      const int lag = p.taps - 1 - j;
+      float u = 0.f;
+      if (lag <= back) u = p.U[(long)(t - lag) * p.ldu + c];
+      else if (lag <= ps) u = st[(long)(back - lag + p.taps - 1) * p.C + c];
+      a = fmaf(bf2f(p.w[(long)c * p.taps + j]), u, a);
+    }
+    p.Y[(long)t * p.ldy + c] = p.act ? silu_exact(a) : a;
+  }
+}
+// after the step: the slot keeps the last taps - 1 inputs of its sequence.  A thread owns a channel; entry j takes
+// what lies `rows` entries further on, so ascending order never overwrites an entry that is still to be read.
+__global__ void conv_state_kernel(ConvP p, const int* __restrict__ seqs) {
+  const int start = seqs[2 * blockIdx.x], rows = seqs[2 * blockIdx.x + 1], n = p.taps - 1;
+  const int p0 = p.pos[start];
+  float* st = p.state + (long)p.slot[start] * p.slot_stride;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.C; c += blockDim.x * gridDim.y)
+    for (int j = 0; j < n; ++j) {
+      const int r = rows - n + j;        // row of the step that holds this input (negative: before the step)
+      float v = 0.f;
+      if (r >= 0) v = p.U[(long)(start + r) * p.ldu + c];
+      else if (p0 + r >= 0) v = st[(long)(j + rows) * p.C + c];
+      st[(long)j * p.C + c] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// rotary on q (in place) and k, and the cache rows of the step: cache[slot][pos] = [k of every kv head | v ...]
+template <typename CT>
+struct QkvPostP {
+  float* Q; long ldq;
+  const float* K; long ldk;
+  const float* V; long ldv;
+  CT* cache; long slot_stride, tok_stride;
+  const int *slot, *pos;
+  const float2* cs;                // [T][rot_dims / 2]
+  int H, G, dim, vdim, rot_dims;
+};
+template <typename CT>
+__global__ void qkv_post_kernel(QkvPostP<CT> p) {
+  const int t = blockIdx.x, half = p.rot_dims / 2;
+  float* q = p.Q + (long)t * p.ldq;
+  for (int e = threadIdx.x; e < p.H * half; e += blockDim.x) {
+    const int h = e / half, i = e % half;
+    const float2 a = p.cs[(long)t * half + i];
+    float* r = q + h * p.dim;
+    const float lo = r[i], hi = r[i + half];
+    r[i] = lo * a.x - hi * a.y;
+    r[i + half] = hi * a.x + lo * a.y;
+  }
+  CT* row = p.cache + (long)p.slot[t] * p.slot_stride + (long)p.pos[t] * p.tok_stride;
+  const float* k = p.K + (long)t * p.ldk;
+  for (int e = threadIdx.x; e < p.G * p.dim; e += blockDim.x) {
+    const int i = e % p.dim;
+    float v;
+    if (i < half) {
+      const float2 a = p.cs[(long)t * half + i];
+      v = k[e] * a.x - k[e + half] * a.y;
+    } else if (i < p.rot_dims) {
+      const float2 a = p.cs[(long)t * half + i - half];
+      v = k[e] * a.x + k[e - half] * a.y;
+    } else {
+      v = k[e];
+    }
+    st_row(row + e, v);
+  }
+  const float* v = p.V + (long)t * p.ldv;
+  for (int e = threadIdx.x; e < p.G * p.vdim; e += blockDim.x) st_row(row + p.G * p.dim + e, v[e]);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// attention of grouped query heads over cached key / value rows.  Block = (query token, kv head x group of up to 8
+// of its query heads, split); a warp per query head.  32 rows are staged at a time (fp32); lane j scores key j, the
+// lanes share the probabilities and each lane accumulates its value columns (online softmax).  The visible keys of a
+// query at position p are lo..p with lo = max(start of p's block of `chunk` positions, p - window + 1, 0).  With a
+// sink, split 0 starts its running maximum at the sink logit with denominator 1: the sink counts once.
+constexpr int SA_KT = 32;
+template <typename CT>
+struct SinkAttnP {
+  const float* q; long ldq;
+  const CT* cache; long slot_stride, tok_stride;
+  const int *slot, *pos;
+  float* out; long ldo;
+  const bf16* sink;
+  int H, G, dim, vdim;
+  float scale;
+  int chunk, window;
+  float* part; int n_split;        // n_split > 1: [T][H][n_split][vdim + 2] = (acc.., max, sum)
+};
+template <typename CT>
+__global__ void sink_attention_kernel(SinkAttnP<CT> p) {
+  extern __shared__ float sm[];
+  const int rep = p.H / p.G, nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hgroups = (rep + nw - 1) / nw;
+  const int t = blockIdx.x, g = blockIdx.y / hgroups, hg = blockIdx.y % hgroups;
+  const bool v4 = (p.dim & 3) == 0;
+  const int dim = p.dim, vdim = p.vdim, ldk = dim + (v4 ? 4 : 1);
+  float* keys = sm;                          // [SA_KT][ldk]
+  float* vals = keys + SA_KT * ldk;          // [SA_KT][vdim]
+  float* qs = vals + SA_KT * vdim;           // [nw][dim]
+  const int hl = hg * nw + warp;
+  const bool live = hl < rep;
+  const int h = g * rep + hl;
+  if (live) {
+    const float* q = p.q + (long)t * p.ldq + (long)h * dim;
+    for (int i = lane; i < dim; i += 32) qs[warp * dim + i] = q[i];
+  }
+  const int ps = p.pos[t];
+  int lo = 0;
+  if (p.chunk > 0) lo = (ps / p.chunk) * p.chunk;
+  if (p.window > 0) lo = max(lo, ps - p.window + 1);
+  const CT* base = p.cache + (long)p.slot[t] * p.slot_stride;
+  const int koff = g * dim, voff = p.G * dim + g * vdim;
+  const int per_lane = (vdim + 31) / 32;
+  float m = -INFINITY, l = 0.f;
+  if (p.sink && blockIdx.z == 0 && live) { m = bf2f(p.sink[h]); l = 1.f; }
+  float acc[8];                              // vdim <= 256
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int k0 = lo + blockIdx.z * SA_KT; k0 <= ps; k0 += SA_KT * p.n_split) {
+    const int nk = min(SA_KT, ps + 1 - k0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nk * dim; e += blockDim.x) {
+      const int j = e / dim, i = e - j * dim;
+      keys[j * ldk + i] = ld_row(base + (long)(k0 + j) * p.tok_stride + koff + i);
+    }
+    for (int e = threadIdx.x; e < nk * vdim; e += blockDim.x) {
+      const int j = e / vdim, i = e - j * vdim;
+      vals[j * vdim + i] = ld_row(base + (long)(k0 + j) * p.tok_stride + voff + i);
+    }
+    __syncthreads();
+    if (!live) continue;
+    float s = -INFINITY;
+    if (lane < nk) {
+      const float* kr = keys + lane * ldk;
+      const float* qr = qs + warp * dim;
+      float a = 0.f;
+      if (v4) {                               // fixed order: four running sums over i mod 4, then (0 + 1) + (2 + 3)
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+        for (int i = 0; i < dim; i += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
+          a0 = fmaf(q4.x, k4.x, a0); a1 = fmaf(q4.y, k4.y, a1); a2 = fmaf(q4.z, k4.z, a2); a3 = fmaf(q4.w, k4.w, a3);
+        }
+        a = (a0 + a1) + (a2 + a3);
+      } else {
+        for (int i = 0; i < dim; ++i) a = fmaf(qr[i], kr[i], a);
+      }
+      s = a * p.scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);       // nothing seen yet: exp(-inf) = 0
+    const float pj = lane < nk ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(pj);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < per_lane) acc[i] *= corr;
+    for (int j = 0; j < nk; ++j) {
+      const float w = __shfl_sync(0xffffffffu, pj, j);
+      const float* vr = vals + j * vdim;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < per_lane) {
+          const int d = lane + 32 * i;
+          if (d < vdim) acc[i] = fmaf(w, vr[d], acc[i]);
+        }
+    }
+  }
+  if (!live) return;
+  if (p.n_split > 1) {                        // un-normalised partial sums; a split without keys: max -inf, sum 0
+    float* o = p.part + (((long)t * p.H + h) * p.n_split + blockIdx.z) * (vdim + 2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < per_lane) {
+        const int d = lane + 32 * i;
+        if (d < vdim) o[d] = acc[i];
+      }
+    if (lane == 0) { o[vdim] = m; o[vdim + 1] = l; }
+    return;
+  }
+  const float inv = 1.0f / l;
+  float* o = p.out + (long)t * p.ldo + (long)h * vdim;
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (i < per_lane) {
+      const int d = lane + 32 * i;
+      if (d < vdim) o[d] = acc[i] * inv;
+    }
+}
+// merge the splits of one (token, head) in a fixed order
+__global__ void sink_attention_merge_kernel(const float* __restrict__ part, int n_split, int vdim,
+                                            float* __restrict__ out, long ldo, int H) {
+  __shared__ float wgt[64];
+  __shared__ float inv_s;
+  const int t = blockIdx.x, h = blockIdx.y, row = vdim + 2;
+  const float* pp = part + ((long)t * H + h) * n_split * row;
+  if (threadIdx.x < 32) {
+    const int s0 = threadIdx.x, s1 = threadIdx.x + 32;
+    const float m0 = s0 < n_split ? pp[(long)s0 * row + vdim] : -INFINITY;
+    const float m1 = s1 < n_split ? pp[(long)s1 * row + vdim] : -INFINITY;
+    const float l0 = s0 < n_split ? pp[(long)s0 * row + vdim + 1] : 0.f;
+    const float l1 = s1 < n_split ? pp[(long)s1 * row + vdim + 1] : 0.f;
+    const float M = warp_max(fmaxf(m0, m1));
+    const float e0 = m0 == -INFINITY ? 0.f : expf(m0 - M), e1 = m1 == -INFINITY ? 0.f : expf(m1 - M);
+    wgt[s0] = e0; wgt[s1] = e1;
+    const float L = warp_sum(l0 * e0 + l1 * e1);
+    if (threadIdx.x == 0) inv_s = 1.0f / L;
+  }
+  __syncthreads();
+  const float inv = inv_s;
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_split; ++s)
+      if (wgt[s] != 0.f) a = fmaf(pp[(long)s * row + d], wgt[s], a);
+    out[(long)t * ldo + (long)h * vdim + d] = a * inv;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// matrix state per head, carried from token to token:  S <- decay S + k u^T,  o = S^T q,  u = v or
+// u = beta (v - (decay S)^T k).  The columns of S evolve independently, so a block owns a slice of the value
+// columns of one head of one sequence and walks the sequence's tokens in order.  A column is held by P threads, each
+// with 32 rows of it in registers (dim <= 32 P); their partial dot products meet in a butterfly over the P lanes.
+// The slot keeps S between steps as [H][32][vdim][P] (row r * 32 + i of column c at ((h * 32 + i) * vdim + c) * P + r),
+// which makes the loads and stores of a warp contiguous; a sequence that starts at position 0 starts from zero.
+// q and k may be shared by `rep` heads, passed through silu, and scaled to unit length per head at load.
+constexpr int LS_CT = 16, LS_THREADS = 128;
+struct StateP {
+  const float* q; long ldq;
+  const float* k; long ldk;
+  const float* v; long ldv;
+  float* out; long ldo;
+  float* state; long slot_stride;
+  const int* seqs;
+  const int *slot, *pos;
+  int H, rep, dim, vdim;
+  int act;                          // silu on q, k, v at load
+  float unit_eps, q_scale;          // unit_eps > 0: q, k <- x / sqrt(sum x^2 + unit_eps); q also times q_scale
+  const float* decay_const;         // [H], or NULL: decay = exp(-exp(A_log[h]) softplus(a[t][h] + dt_bias[h]))
+  const float* a; long lda;
+  const bf16 *A_log, *dt_bias;
+  const float* b; long ldb;         // beta = sigmoid(b[t][h]); NULL: 1
+  int delta;
+};
+template <int P>
+__global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
+  constexpr int CB = LS_THREADS / P, LD = P * 33;
+  __shared__ float ks[LS_CT][LD], qs[LS_CT][LD];
+  __shared__ float vs[LS_CT][CB];
+  __shared__ float dec[LS_CT], bet[LS_CT];
+  const int start = p.seqs[2 * blockIdx.x], rows = p.seqs[2 * blockIdx.x + 1];
+  const int h = blockIdx.y, hk = h / p.rep;
+  const int cj = threadIdx.x / P, r = threadIdx.x % P, col = blockIdx.z * CB + cj;
+  const bool valid = col < p.vdim;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float S[32];
+  float* st = p.state + (long)p.slot[start] * p.slot_stride;
+  if (p.pos[start] > 0 && valid) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) S[i] = st[(((long)h * 32 + i) * p.vdim + col) * P + r];
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) S[i] = 0.f;
+  }
+  for (int e = threadIdx.x; e < LS_CT * LD; e += LS_THREADS) { (&ks[0][0])[e] = 0.f; (&qs[0][0])[e] = 0.f; }
+  for (int c0 = 0; c0 < rows; c0 += LS_CT) {
+    const int nc = min(LS_CT, rows - c0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nc * p.dim; e += LS_THREADS) {
+      const int tk = e / p.dim, i = e - tk * p.dim;
+      const long t = start + c0 + tk;
+      float kv = p.k[t * p.ldk + (long)hk * p.dim + i], qv = p.q[t * p.ldq + (long)hk * p.dim + i];
+      if (p.act) { kv = silu_exact(kv); qv = silu_exact(qv); }
+      ks[tk][(i >> 5) * 33 + (i & 31)] = kv;
+      qs[tk][(i >> 5) * 33 + (i & 31)] = qv;
+    }
+    for (int e = threadIdx.x; e < nc * CB; e += LS_THREADS) {
+      const int tk = e / CB, c = e - tk * CB, cc = blockIdx.z * CB + c;
+      float vv = cc < p.vdim ? p.v[(long)(start + c0 + tk) * p.ldv + (long)h * p.vdim + cc] : 0.f;
+      vs[tk][c] = p.act ? silu_exact(vv) : vv;
+    }
+    if (threadIdx.x < nc) {
+      const long t = start + c0 + threadIdx.x;
+      dec[threadIdx.x] = p.decay_const ? p.decay_const[h]
+          : expf(-expf(bf2f(p.A_log[h])) * softplus_exact(p.a[t * p.lda + h] + bf2f(p.dt_bias[h])));
+      bet[threadIdx.x] = p.b ? sigmoid_exact(p.b[t * p.ldb + h]) : 1.f;
+    }
+    __syncthreads();
+    if (p.unit_eps > 0.f) {                   // a warp per token row: lengths in a fixed order, then the scaling
+      for (int tk = warp; tk < nc; tk += LS_THREADS / 32) {
+        float sk = 0.f, sq = 0.f;
+        for (int i = lane; i < p.dim; i += 32) {
+          const float a = ks[tk][(i >> 5) * 33 + (i & 31)], b = qs[tk][(i >> 5) * 33 + (i & 31)];
+          sk = fmaf(a, a, sk); sq = fmaf(b, b, sq);
+        }
+        const float ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps), iq = p.q_scale / sqrtf(warp_sum(sq) + p.unit_eps);
+        for (int i = lane; i < p.dim; i += 32) {
+          ks[tk][(i >> 5) * 33 + (i & 31)] *= ik;
+          qs[tk][(i >> 5) * 33 + (i & 31)] *= iq;
+        }
+      }
+      __syncthreads();
+    }
+    for (int tk = 0; tk < nc; ++tk) {
+      const float* kr = &ks[tk][r * 33];
+      const float* qr = &qs[tk][r * 33];
+      const float d = dec[tk];
+      float u = vs[tk][cj];
+      if (p.delta) {
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dot = fmaf(S[i], kr[i], dot);
+#pragma unroll
+        for (int o = 1; o < P; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        u = bet[tk] * (u - d * dot);
+      }
+      float o_ = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        S[i] = fmaf(kr[i], u, d * S[i]);
+        o_ = fmaf(S[i], qr[i], o_);
+      }
+#pragma unroll
+      for (int o = 1; o < P; o <<= 1) o_ += __shfl_xor_sync(0xffffffffu, o_, o);
+      if (r == 0 && valid) p.out[(long)(start + c0 + tk) * p.ldo + (long)h * p.vdim + col] = o_;
+    }
+  }
+  if (valid) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) st[(((long)h * 32 + i) * p.vdim + col) * P + r] = S[i];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// what follows a mixer's heads, written into a column range of the buffer the output projection reads:
+//   out[t][c] = scale * o[t][c] * [ rsqrt(mean over its group of `span` numbers + eps) * w[c mod w_len] ] * act(gate)
+// with the gate one number per element or per head, through a sigmoid or silu.  A warp per norm group.
+struct HeadPostP {
+  const float* o; long ldi;
+  const float* gate; long ldg;
+  const bf16* w; int w_len;
+  float eps; int span;             // 0: no norm
+  int gate_per_head, gate_silu, dv, n;
+  float scale;
+  float* out; long ldo;
+};
+__global__ void head_post_kernel(HeadPostP p) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int span = p.span > 0 ? p.span : p.dv, groups = p.n / span;
+  const float* o = p.o + (long)t * p.ldi;
+  const float* g = p.gate ? p.gate + (long)t * p.ldg : nullptr;
+  float* out = p.out + (long)t * p.ldo;
+  for (int gi = warp; gi < groups; gi += nw) {
+    float inv = 1.f;
+    if (p.span > 0) {
+      float ss = 0.f;
+      for (int i = lane; i < span; i += 32) { const float v = o[gi * span + i]; ss = fmaf(v, v, ss); }
+      inv = 1.0f / sqrtf(warp_sum(ss) / (float)span + p.eps);
+    }
+    for (int i = lane; i < span; i += 32) {
+      const int c = gi * span + i;
+      float v = o[c] * inv;
+      if (p.w) v *= bf2f(p.w[c % p.w_len]);
+      if (g) {
+        const float z = g[p.gate_per_head ? c / p.dv : c];
+        v *= p.gate_silu ? silu_exact(z) : sigmoid_exact(z);
+      }
+      out[c] = v * p.scale;
+    }
+  }
+}
+
+// gated feed-forward activation with clamps: g = min(a, lim), u = clamp(b, -lim, lim), y = g sigmoid(alpha g) (u + 1)
+__global__ void glu_clamp_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
+                                 float alpha, float* __restrict__ Y, long ldy, int n) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float g = fminf(G[(long)t * ldg + i], lim);
+    const float u = fminf(fmaxf(U[(long)t * ldu + i], -lim), lim);
+    Y[(long)t * ldy + i] = g * sigmoid_exact(alpha * g) * (u + 1.0f);
+  }
+}
+
+unsigned long long g_sink_attr_f32 = 0, g_sink_attr_bf16 = 0;
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
+                       const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
+                       int act, int T, void* st) {
+  B200_REQUIRE(U && w && Y && state && slot && pos && first && seqs && T > 0 && n_seq > 0 && C > 0 && taps > 0,
+               "lm_short_conv: bad argument");
+  ConvP p{U, ldu, (const bf16*)w, Y, ldy, state, slot_stride, slot, pos, first, C, taps, act};
+  const int by = cdiv(C, 256) < 8 ? cdiv(C, 256) : 8;
+  short_conv_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(p);
+  B200_CHECK_LAUNCH();
+  if (taps > 1) {
+    conv_state_kernel<<<dim3(n_seq, by), 256, 0, (cudaStream_t)st>>>(p, seqs);
+    B200_CHECK_LAUNCH();
+  }
+  return B200_OK;
+}
+
+int b200_lm_qkv_post(float* Q, long ldq, const float* K, long ldk, const float* V, long ldv, void* cache, int cache_bf16,
+                     long slot_stride, long tok_stride, const int* slot, const int* pos, const float* cs, int H, int G,
+                     int dim, int vdim, int rot_dims, int T, void* st) {
+  B200_REQUIRE(Q && K && V && cache && slot && pos && T > 0 && H > 0 && G > 0, "lm_qkv_post: bad argument");
+  B200_REQUIRE(rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || cs), "lm_qkv_post: rotated dims %d of %d", rot_dims, dim);
+  if (cache_bf16) {
+    QkvPostP<bf16> p{Q, ldq, K, ldk, V, ldv, (bf16*)cache, slot_stride, tok_stride, slot, pos, (const float2*)cs, H, G, dim, vdim, rot_dims};
+    qkv_post_kernel<bf16><<<T, 256, 0, (cudaStream_t)st>>>(p);
+  } else {
+    QkvPostP<float> p{Q, ldq, K, ldk, V, ldv, (float*)cache, slot_stride, tok_stride, slot, pos, (const float2*)cs, H, G, dim, vdim, rot_dims};
+    qkv_post_kernel<float><<<T, 256, 0, (cudaStream_t)st>>>(p);
+  }
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cache_bf16, long slot_stride, long tok_stride,
+                           const int* slot, const int* pos, float* out, long ldo, const void* sink, int H, int G,
+                           int dim, int vdim, float scale, int chunk, int window, float* part, int n_split, int T,
+                           void* st) {
+  B200_REQUIRE(q && cache && slot && pos && out && T > 0 && H > 0 && G > 0 && H % G == 0, "lm_sink_attention: bad argument");
+  B200_REQUIRE(vdim <= 256, "lm_sink_attention: value size %d not supported", vdim);
+  if (n_split < 1 || !part) n_split = 1;
+  B200_REQUIRE(n_split <= 64, "lm_sink_attention: at most 64 splits");
+  const int rep = H / G, nw = rep < 8 ? rep : 8;
+  const size_t smem = ((size_t)SA_KT * (dim + ((dim & 3) == 0 ? 4 : 1)) + (size_t)SA_KT * vdim + (size_t)nw * dim) * sizeof(float);
+  B200_REQUIRE(smem <= 200 * 1024, "lm_sink_attention: rows of %d + %d numbers do not fit shared memory", dim, vdim);
+  dim3 grid(T, G * cdiv(rep, nw), n_split);
+  if (cache_bf16) {
+    if (first_use_on_device(&g_sink_attr_bf16))
+      B200_CUDA(cudaFuncSetAttribute(sink_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SinkAttnP<bf16> p{q, ldq, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split};
+    sink_attention_kernel<bf16><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
+  } else {
+    if (first_use_on_device(&g_sink_attr_f32))
+      B200_CUDA(cudaFuncSetAttribute(sink_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SinkAttnP<float> p{q, ldq, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split};
+    sink_attention_kernel<float><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
+  }
+  B200_CHECK_LAUNCH();
+  if (n_split > 1) {
+    const int mt = vdim >= 256 ? 256 : (vdim + 31) / 32 * 32;
+    sink_attention_merge_kernel<<<dim3(T, H), mt, 0, (cudaStream_t)st>>>(part, n_split, vdim, out, ldo, H);
+    B200_CHECK_LAUNCH();
+  }
+  return B200_OK;
+}
+
+int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv, float* out, long ldo,
+                         float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
+                         int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
+                         const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
+                         const float* b, long ldb, int delta, void* st) {
+  B200_REQUIRE(q && k && v && out && state && seqs && slot && pos && n_seq > 0 && H > 0 && rep > 0 && H % rep == 0,
+               "lm_linear_state: bad argument");
+  B200_REQUIRE(dim > 0 && dim <= 256 && vdim > 0, "lm_linear_state: key size %d not supported (at most 256)", dim);
+  B200_REQUIRE(decay_const || (a && A_log && dt_bias), "lm_linear_state: a decay per head, or the inputs of a computed one");
+  StateP p{q, ldq, k, ldk, v, ldv, out, ldo, state, slot_stride, seqs, slot, pos, H, rep, dim, vdim, act, unit_eps, q_scale,
+           decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta};
+  const cudaStream_t cs = (cudaStream_t)st;
+  if (dim <= 32) linear_state_kernel<1><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS)), LS_THREADS, 0, cs>>>(p);
+  else if (dim <= 64) linear_state_kernel<2><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 2)), LS_THREADS, 0, cs>>>(p);
+  else if (dim <= 128) linear_state_kernel<4><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 4)), LS_THREADS, 0, cs>>>(p);
+  else linear_state_kernel<8><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 8)), LS_THREADS, 0, cs>>>(p);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, const void* w, int w_len, float eps, int span,
+                      int gate_per_head, int gate_silu, int dv, int n, float scale, float* out, long ldo, int T, void* st) {
+  B200_REQUIRE(o && out && T > 0 && n > 0 && dv > 0 && n % dv == 0, "lm_head_post: bad argument");
+  B200_REQUIRE(span == 0 || n % span == 0, "lm_head_post: norm groups of %d numbers in rows of %d", span, n);
+  B200_REQUIRE(!w || w_len > 0, "lm_head_post: a weight needs its length");
+  HeadPostP p{o, ldi, gate, ldg, (const bf16*)w, w_len, eps, span, gate_per_head, gate_silu, dv, n, scale, out, ldo};
+  head_post_kernel<<<T, 256, 0, (cudaStream_t)st>>>(p);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float* Y, long ldy,
+                      int n, int T, void* st) {
+  B200_REQUIRE(G && U && Y && T > 0 && n > 0, "lm_glu_clamp: bad argument");
+  glu_clamp_kernel<<<T, 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, Y, ldy, n);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+}  // extern "C"

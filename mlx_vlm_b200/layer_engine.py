@@ -98,11 +98,19 @@ class LayerEngine:
                 x = embeds.to(torch.float32).reshape(-1, c.width).clone()
         else:
             x = ops.embed(tokens, c.embed, c.embed_scale)
-        for layer in c.layers:
-            layer.forward(ctx, x)
+        if hasattr(c, "run_layers"):      # a design with its own order of layer runs (a span that repeats)
+            def embed_again():
+                if embeds is not None:
+                    with torch.cuda.stream(self.stream):
+                        return embeds.to(torch.float32).reshape(-1, c.width).clone()
+                return ops.embed(tokens, c.embed, c.embed_scale)
+            x = c.run_layers(ctx, x, embed_again)
+        else:
+            for layer in c.layers:
+                layer.forward(ctx, x)
         n = x.shape[0] if want is None else want.shape[0]
         xn = ops.empty((n, c.width))
-        ops.norm_rows(x, c.final_norm, c.eps, xn, w_offset=1.0, rows=want)
+        ops.norm_rows(x, c.final_norm, c.eps, xn, w_offset=getattr(c, "norm_offset", 1.0), rows=want)
         cap = c.logit_softcap
         return ops.linear(xn, c.head, epi=EPI_SOFTCAP if cap else EPI_NONE, epi_param=cap or 0.0)
 
@@ -162,7 +170,8 @@ class LayerEngine:
                 self.ops.advance_rows(self._sampled[:B], self._tok, self._pos, None, self._log.view(-1, 1), self._lstep)
             return logits
 
-        key = (batch, B, self.pool.buf.data_ptr(), self.pool.capacity)
+        state = getattr(self.pool, "state", None)      # a pool with recurrent state: its buffer is an argument too
+        key = (batch, B, self.pool.buf.data_ptr(), self.pool.capacity, 0 if state is None else state.data_ptr())
         if not self.use_graphs:
             self._logits = body()
         elif key in self._graphs:

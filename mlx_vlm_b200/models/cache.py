@@ -77,6 +77,33 @@ class LatentPool(KVPool):
             self.buf[:, dst, :n_tokens].copy_(src_pool.buf[:, src, :n_tokens])
 
 
+class StatePool(LatentPool):
+    """Pool of a design that mixes attention with recurrent layers.  Beside the rows of the caching layers (one row
+    of `row_dim` numbers per token: the keys of all key/value heads, then their values; a layer with shorter rows
+    uses the front of the row) every slot owns `state_floats` fp32 numbers: the matrix states of the recurrent layers
+    and the last inputs of the short convolutions, each layer at its own offset.  The state does not grow with the
+    sequence.  A sequence that starts at position 0 never reads its slot's state, so a released slot is handed to the
+    next request as it is."""
+
+    def __init__(self, n_layers: int, row_dim: int, state_floats: int, device, batch: int = 1, capacity: int = 0,
+                 dtype=torch.bfloat16):
+        self.state_floats = int(state_floats)
+        self.state = torch.zeros((batch, max(self.state_floats, 1)), dtype=torch.float32, device=device)
+        super().__init__(max(n_layers, 1), max(row_dim, 1), device, batch=batch, capacity=capacity, dtype=dtype)
+
+    def add_slots(self, batch: int, live_tokens: int):
+        old_rows = self.batch
+        if not super().add_slots(batch, live_tokens):
+            return False
+        old, self.state = self.state, torch.zeros((batch, self.state.shape[1]), dtype=torch.float32, device=self.device)
+        self.state[:old_rows].copy_(old)
+        return True
+
+    def copy_slot(self, dst: int, src_pool: "StatePool", src: int, n_tokens: int):
+        super().copy_slot(dst, src_pool, src, n_tokens)
+        self.state[dst].copy_(src_pool.state[src])
+
+
 class SlotTable:
     """Which slots of a pool are in use: the lowest free slot is handed out first, a released slot is
     used again by the next request."""
@@ -289,6 +316,65 @@ class LatentCache(_BaseCache):
     def nbytes(self):
         k = self.keys
         return 0 if k is None or self.shared else k.numel() * k.element_size()
+
+
+class RunCache(_BaseCache):
+    """What ONE run of a layer keeps for ONE request in a `StatePool` slot: the rows of its attention (if it has
+    one) and its span of the slot's state (if it is recurrent), with the `KVCache` surface the generation loops use.
+    A layer that runs several times (a repeated span of layers) has one of these per run.  A recurrent state cannot be
+    rolled back, so such a cache is not trimmable."""
+
+    def __init__(self, pool: StatePool, row: int = 0, kv_layer: Optional[int] = None, kv_dim: int = 0,
+                 state_off: int = 0, state_len: int = 0):
+        self._pool, self._row, self._layer = pool, row, kv_layer
+        self._kv_dim, self._state_off, self._state_len = kv_dim, state_off, state_len
+        self.offset = 0
+
+    @property
+    def keys(self):
+        if self._layer is None or self._pool.buf is None:
+            return None
+        return self._pool.buf[self._layer, self._row:self._row + 1, :, :self._kv_dim]
+
+    @property
+    def values(self):
+        return self.keys
+
+    @property
+    def recurrent(self):
+        """this run's span of the slot's state (fp32), or None"""
+        if not self._state_len:
+            return None
+        return self._pool.state[self._row, self._state_off:self._state_off + self._state_len]
+
+    @property
+    def state(self):
+        k = self.keys
+        return (None if k is None else k[:, :self.offset]), self.recurrent
+
+    def size(self):
+        return self.offset
+
+    def is_trimmable(self):
+        return self._state_len == 0
+
+    def trim(self, n):
+        if not self.is_trimmable():
+            return 0
+        n = min(self.offset, n)
+        self.offset -= n
+        return n
+
+    def empty(self):
+        return self.offset == 0
+
+    def make_mask(self, N: int, return_array: bool = False, window_size=None):
+        return None if N == 1 else "causal"
+
+    @property
+    def nbytes(self):
+        k = self.keys
+        return (0 if k is None else k.numel() * k.element_size()) + 4 * self._state_len
 
 
 def make_prompt_cache(model: Any, max_kv_size: Optional[int] = None) -> List[Any]:

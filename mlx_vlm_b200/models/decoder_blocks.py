@@ -5,6 +5,15 @@ parameters, its packed weight layout and its launch sequence over the layer ops 
   feed-forwards  FEEDFORWARDS["moe"]         -> ExpertMixture
   layer          PostNormLayer: x += norm(mixer(x)); x += norm(ff(x)), weights of the norms stored around zero
 
+and, for layers whose sublayers all read ONE normed input (so that all their input projections are one product and
+all their output projections another), the parts of a `SharedInputLayer`:
+
+  mixers         FUSED_MIXERS["attention"]  -> SinkAttention   (grouped heads, sink logit, block-local keys, gate)
+                 FUSED_MIXERS["lightning"]  -> DecayedState    (outer-product state with a fixed decay per head)
+                 FUSED_MIXERS["parallel"]   -> an attention and a GatedDeltaRule side by side, weighted
+  feed-forwards  FUSED_FEEDFORWARDS["dense"] -> ClampedGLU
+  layer          SharedInputLayer: n = norm(x); x += sum of the parts' outputs
+
 A block declares `manifest(prefix)` (packed name, shape) and `pack(prefix, checkpoint tensors, arena)`; the model
 packs all blocks into ONE device arena (the layout the other models of this package use).  `forward(ctx, x)`
 enqueues the block's kernels; `ctx` carries the per-token slot / position arrays of the step and the cache pool,
@@ -30,6 +39,14 @@ class StepCtx:
     eps: float
     segments: Optional[List] = None   # host view of the step: (first token, tokens, slot, first position) per request
     _rope: Dict = field(default_factory=dict)
+    _seq: Optional[tuple] = None
+
+    def seq_tables(self):
+        """(first (T,), seqs (G, 2), G): the sequences of the step for the mixers that walk them in order; without a
+        host view every token is a sequence of its own (a decode step)"""
+        if self._seq is None:
+            self._seq = self.ops.seq_tables(self.segments, self.pos.shape[0])
+        return self._seq
 
     def rope(self, base: float, dims: int) -> torch.Tensor:
         key = (float(base), int(dims))
@@ -275,6 +292,284 @@ class PostNormLayer:
         if self.ff is not None:
             rows, wgt = self.ff.forward(ctx, x)
             ops.norm_rows(rows, self.w["norm2"], ctx.eps, x, w_offset=1.0, add=True, combine=wgt, top=self.ff.top)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Parts of a layer whose sublayers share their input.  A part names the rows it adds to the layer's input projection
+# (`in_names`, stacked in that order; `n_in` rows in all), the columns it adds to the output projection (`out_name`,
+# `n_out`), its other tensors (`small`), what it keeps per request (`kv_dim` numbers per cached token, `state_floats`
+# fp32 numbers per slot), and `forward(ctx, D, cat, kv_layer, state_off, out_scale)`: D (T, n_in) its columns of the
+# projected rows (scratch: it may overwrite them), cat (T, n_out) its columns of the output projection's input.
+class SinkAttention:
+    """Softmax attention with `heads` query heads over `kv_heads` key/value heads (query head h reads key/value head
+    h // (heads / kv_heads)), rotate-half rotary on the first `rot.dims` numbers of every query and key head, an
+    optional short causal convolution on q, k, v before the rotation (`conv` taps), keys limited to the query's own
+    block of `mask.size` positions (absent: all earlier positions), a learned logit per head that joins the softmax's
+    denominator without a key or a value (`sink`), and a sigmoid gate on the heads' outputs computed from the layer's
+    input: one number per output element (`gate="element"`) or per head (`gate="head"`)."""
+
+    def __init__(self, index: int, cfg: dict, width: int, gate: str = "element"):
+        self.index, self.W, self.gate = index, width, gate
+        self.H, self.G, self.dim, self.vdim = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
+        if self.H % self.G:
+            raise ValueError(f"layer {index}: {self.H} query heads do not divide over {self.G} key/value heads")
+        self.scale = float(cfg["scale"])
+        rot = cfg.get("rot") or {}
+        self.rot_base, self.rot_dims = float(rot.get("base", 10000.0)), int(rot.get("dims", 0))
+        self.chunk = int((cfg.get("mask") or {}).get("size", 0))
+        self.window = int(cfg.get("window", 0))
+        self.taps = int(cfg.get("conv") or 0)
+        self.n_q, self.n_k, self.n_v = self.H * self.dim, self.G * self.dim, self.G * self.vdim
+        self.n_gate = self.H * self.vdim if gate == "element" else self.H
+        self.in_names, self.out_name = ["q", "k", "v", "g"], "o"
+        self.n_in, self.n_out = self.n_q + self.n_k + self.n_v + self.n_gate, self.H * self.vdim
+        self.kv_dim = self.n_k + self.n_v
+        self.state_floats = max(self.taps - 1, 0) * (self.n_q + self.n_k + self.n_v)
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def in_rows(self, name: str) -> int:
+        return {"q": self.n_q, "k": self.n_k, "v": self.n_v, "g": self.n_gate}[name]
+
+    def small(self):
+        out = [("sink", (self.H,))]
+        if self.taps:
+            out.append(("conv", (self.n_q + self.n_k + self.n_v, self.taps)))
+        return out
+
+    def checkpoint_small(self):
+        """packed name -> the checkpoint tensors it is stacked from"""
+        out = {"sink": ["sink"]}
+        if self.taps:
+            out["conv"] = ["q.conv", "k.conv", "v.conv"]
+        return out
+
+    def forward(self, ctx: StepCtx, D, cat, kv_layer: int, state_off: int, out_scale: float = 1.0):
+        ops, w, T = ctx.ops, self.w, D.shape[0]
+        nq, nk, nv = self.n_q, self.n_k, self.n_v
+        src = D
+        if self.taps:
+            src = ops.short_conv(D[:, :nq + nk + nv], w["conv"], ctx.pool.state[:, state_off:state_off + self.state_floats],
+                                 ctx)
+        q, k, v = src[:, :nq], src[:, nq:nq + nk], src[:, nq + nk:nq + nk + nv]
+        rows = ctx.pool.buf[kv_layer][..., :self.kv_dim]
+        ops.qkv_post(q, k, v, rows, ctx.slot, ctx.pos, ctx.rope(self.rot_base, self.rot_dims), self.H, self.G, self.dim,
+                     self.vdim, self.rot_dims)
+        o = ops.empty((T, self.n_out))
+        ops.sink_attention(q, rows, ctx.slot, ctx.pos, o, w["sink"], self.H, self.G, self.dim, self.vdim, self.scale,
+                           chunk=self.chunk, window=self.window, n_split=1 if ctx.segments is not None and T > 16 else None)
+        ops.head_post(o, cat, dv=self.vdim, gate=D[:, nq + nk + nv:], gate_per_head=self.gate == "head", scale=out_scale)
+
+
+def state_lanes(dim: int) -> int:
+    """threads that share a column of a matrix state (32 rows each): the layout of the state in the slot"""
+    if dim > 256:
+        raise ValueError(f"a matrix state with {dim} rows is not supported (at most 256)")
+    return 1 if dim <= 32 else 2 if dim <= 64 else 4 if dim <= 128 else 8
+
+
+class GatedDeltaRule:
+    """Gated delta rule: per head a (dim, vdim) state with  S <- g S;  S <- S + k (beta (v - S^T k))^T;  o = S^T q.
+    q, k (`kv_heads` heads, shared by heads / kv_heads value heads) and v pass a short causal convolution and silu; q, k
+    are then scaled to unit length (q also by dim^-1/2); beta = sigmoid(W_b n); g = exp(-exp(A_log) softplus(W_a n +
+    dt_bias)); every head's output is RMS-normed over vdim, weighted, and gated by silu(W_g n)."""
+
+    def __init__(self, index: int, cfg: dict, width: int, unit_eps: float = 1e-6):
+        self.index, self.W, self.unit_eps = index, width, unit_eps
+        self.H, self.G, self.dim, self.vdim, self.taps = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"], int(cfg["conv"])
+        if self.H % self.G:
+            raise ValueError(f"layer {index}: {self.H} value heads do not divide over {self.G} query/key heads")
+        self.n_qk, self.n_v = self.G * self.dim, self.H * self.vdim
+        self.n_conv = 2 * self.n_qk + self.n_v
+        self.in_names, self.out_name = ["q", "k", "v", "b", "a", "g"], "o"
+        self.n_in, self.n_out = self.n_conv + 2 * self.H + self.n_v, self.n_v
+        self.kv_dim = 0
+        self.conv_floats = max(self.taps - 1, 0) * self.n_conv
+        self.state_floats = self.conv_floats + self.H * 32 * self.vdim * state_lanes(self.dim)
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def in_rows(self, name: str) -> int:
+        return {"q": self.n_qk, "k": self.n_qk, "v": self.n_v, "b": self.H, "a": self.H, "g": self.n_v}[name]
+
+    def small(self):
+        return [("conv", (self.n_conv, self.taps)), ("A_log", (self.H,)), ("dt_bias", (self.H,)), ("norm", (self.vdim,))]
+
+    def checkpoint_small(self):
+        return {"conv": ["q.conv", "k.conv", "v.conv"], "A_log": ["A_log"], "dt_bias": ["dt_bias"], "norm": ["norm"]}
+
+    def forward(self, ctx: StepCtx, D, cat, kv_layer: int, state_off: int, out_scale: float = 1.0):
+        ops, w, T = ctx.ops, self.w, D.shape[0]
+        n, nc, H = self.n_qk, self.n_conv, self.H
+        st = ctx.pool.state
+        c = ops.short_conv(D[:, :nc], w["conv"], st[:, state_off:state_off + self.conv_floats], ctx, act=True)
+        o = ops.empty((T, self.n_out))
+        ops.linear_state(c[:, :n], c[:, n:2 * n], c[:, 2 * n:], o, st[:, state_off + self.conv_floats:state_off + self.state_floats],
+                         ctx, H=H, rep=H // self.G, dim=self.dim, vdim=self.vdim, unit_eps=self.unit_eps,
+                         q_scale=float(self.dim) ** -0.5, a=D[:, nc + H:nc + 2 * H], A_log=w["A_log"], dt_bias=w["dt_bias"],
+                         b=D[:, nc:nc + H], delta=True)
+        ops.head_post(o, cat, dv=self.vdim, gate=D[:, nc + 2 * H:], gate_silu=True, w=w["norm"], eps=ctx.eps, span=self.vdim,
+                      scale=out_scale)
+
+
+class DecayedState:
+    """Outer-product state with a fixed decay per head:  S <- decay_h S + k v^T,  o = S^T q,  q, k, v = silu of their
+    projections; the heads' outputs are RMS-normed together, weighted, and gated by sigmoid(W_g n)."""
+
+    def __init__(self, index: int, cfg: dict, width: int):
+        self.index, self.W = index, width
+        self.H, self.dim, self.vdim = cfg["heads"], cfg["dim"], cfg["vdim"]
+        self.decay = [float(d) for d in cfg["decay"]]
+        if len(self.decay) != self.H:
+            raise ValueError(f"layer {index}: {len(self.decay)} decays for {self.H} heads")
+        self.n_qk, self.n_v = self.H * self.dim, self.H * self.vdim
+        self.in_names, self.out_name = ["q", "k", "v", "g"], "o"
+        self.n_in, self.n_out = 2 * self.n_qk + 2 * self.n_v, self.n_v
+        self.kv_dim = 0
+        self.state_floats = self.H * 32 * self.vdim * state_lanes(self.dim)
+        self.w: Dict[str, torch.Tensor] = {}
+        self._decay_dev = None
+
+    def in_rows(self, name: str) -> int:
+        return {"q": self.n_qk, "k": self.n_qk, "v": self.n_v, "g": self.n_v}[name]
+
+    def small(self):
+        return [("norm", (self.n_v,))]
+
+    def checkpoint_small(self):
+        return {"norm": ["norm"]}
+
+    def forward(self, ctx: StepCtx, D, cat, kv_layer: int, state_off: int, out_scale: float = 1.0):
+        ops, T = ctx.ops, D.shape[0]
+        n, nv = self.n_qk, self.n_v
+        if self._decay_dev is None:       # first used by a prompt step, never inside a captured decode step
+            import numpy as np
+            self._decay_dev = ops.to_device(np.asarray(self.decay, dtype=np.float32), np.float32)
+        o = ops.empty((T, nv))
+        ops.linear_state(D[:, :n], D[:, n:2 * n], D[:, 2 * n:2 * n + nv], o,
+                         ctx.pool.state[:, state_off:state_off + self.state_floats], ctx, H=self.H, rep=1, dim=self.dim,
+                         vdim=self.vdim, act=True, decay_const=self._decay_dev)
+        ops.head_post(o, cat, dv=self.vdim, gate=D[:, 2 * n + nv:], w=self.w["norm"], eps=ctx.eps, span=nv, scale=out_scale)
+
+
+class ClampedGLU:
+    """Gated feed-forward with clamps: g = min(W_gate n, limit), u = clamp(W_up n, -limit, limit),
+    W_down (g sigmoid(alpha g) (u + 1))."""
+
+    def __init__(self, index: int, cfg: dict, width: int, alpha: float = 1.702):
+        self.index, self.W, self.alpha = index, width, alpha
+        self.ff, self.limit = int(cfg["ff"]), float(cfg["limit"])
+        self.in_names, self.out_name = ["gate", "up"], "down"
+        self.n_in, self.n_out = 2 * self.ff, self.ff
+        self.kv_dim = self.state_floats = 0
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def in_rows(self, name: str) -> int:
+        return self.ff
+
+    def small(self):
+        return []
+
+    def checkpoint_small(self):
+        return {}
+
+    def forward(self, ctx: StepCtx, D, cat, kv_layer: int, state_off: int, out_scale: float = 1.0):
+        ctx.ops.glu_clamp(D[:, :self.ff], D[:, self.ff:], self.limit, self.alpha, cat)
+
+
+def _side_by_side(index: int, cfg: dict, width: int):
+    """an attention (gate per head) and a gated delta rule reading the same input; their outputs are weighted"""
+    return [("left.", SinkAttention(index, cfg["left"], width, gate="head"), float(cfg["left_scale"])),
+            ("right.", GatedDeltaRule(index, cfg["right"], width), float(cfg["right_scale"]))]
+
+
+FUSED_MIXERS = {"attention": lambda i, c, w: [("", SinkAttention(i, c, w, gate="element"), 1.0)],
+                "lightning": lambda i, c, w: [("", DecayedState(i, c, w), 1.0)],
+                "parallel": _side_by_side}
+FUSED_FEEDFORWARDS = {"dense": ClampedGLU}
+
+
+class SharedInputLayer:
+    """n = rmsnorm(x) * w;  x <- x + sum_parts scale_part * part(n).  The parts' input projections are stacked into ONE
+    weight (one product per layer gives every part its rows), their output projections are laid side by side into ONE
+    weight whose input is the parts' outputs side by side — the sum over the parts and the residual add happen inside
+    that product.  A part's scale is applied to its output before the product."""
+
+    def __init__(self, index: int, cfg: dict, width: int):
+        self.index, self.W = index, width
+        if cfg["type"] not in FUSED_MIXERS:
+            raise ValueError(f"layer {index}: unknown mixer type {cfg['type']!r} (have {sorted(FUSED_MIXERS)})")
+        self.parts = [("mix." + p, part, s) for p, part, s in FUSED_MIXERS[cfg["type"]](index, cfg["mixer"], width)]
+        f = cfg.get("mlp")
+        if f is not None:
+            if f.get("kind") not in FUSED_FEEDFORWARDS:
+                raise ValueError(f"layer {index}: unknown feed-forward kind {f.get('kind')!r} (have {sorted(FUSED_FEEDFORWARDS)})")
+            self.parts.append(("mlp.", FUSED_FEEDFORWARDS[f["kind"]](index, f, width), 1.0))
+        self.n_in = sum(part.n_in for _, part, _ in self.parts)
+        self.n_out = sum(part.n_out for _, part, _ in self.parts)
+        self.kv_layers = sum(1 for _, part, _ in self.parts if part.kv_dim)
+        self.kv_dim = max(part.kv_dim for _, part, _ in self.parts)
+        self.state_floats = sum(part.state_floats for _, part, _ in self.parts)
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def manifest(self, p: str):
+        out = [(p + "norm1", (self.W,)), (p + "in", (self.n_in, self.W)), (p + "out", (self.W, self.n_out))]
+        for pre, part, _ in self.parts:
+            out += [(p + pre + n, shape) for n, shape in part.small()]
+        return out
+
+    def checkpoint_tensors(self, p: str):
+        """checkpoint name -> shape of everything this layer reads"""
+        out = {p + "norm1": (self.W,)}
+        for pre, part, _ in self.parts:
+            for n in part.in_names:
+                out[p + pre + n] = (part.in_rows(n), self.W)
+            out[p + pre + part.out_name] = (self.W, part.n_out)
+            shapes = dict(part.small())
+            for packed, names in part.checkpoint_small().items():
+                if len(names) == 1:
+                    out[p + pre + names[0]] = shapes[packed]
+                else:       # the convolutions of q, k, v stacked: rows split like the projections'
+                    for n in names:
+                        out[p + pre + n] = (part.in_rows(n.split(".")[0]), shapes[packed][1])
+        return out
+
+    def pack(self, p: str, ck, view):
+        view(p + "norm1").copy_(ck[p + "norm1"])
+        w_in, w_out = view(p + "in"), view(p + "out")
+        r = c = 0
+        for pre, part, _ in self.parts:
+            for n in part.in_names:
+                t = ck[p + pre + n]
+                w_in[r:r + t.shape[0]].copy_(t)
+                r += t.shape[0]
+            w_out[:, c:c + part.n_out].copy_(ck[p + pre + part.out_name])
+            c += part.n_out
+            for packed, names in part.checkpoint_small().items():
+                dst, at = view(p + pre + packed), 0
+                for n in names:
+                    t = ck[p + pre + n]
+                    dst[at:at + t.shape[0]].copy_(t)
+                    at += t.shape[0]
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n: view(p + n) for n in ("norm1", "in", "out")}
+        for pre, part, _ in self.parts:
+            part.w = {n: view(p + pre + n) for n, _ in part.small()}
+
+    def forward(self, ctx: StepCtx, x: torch.Tensor, kv_base: int = 0, state_base: int = 0):
+        """kv_base: the pool's caching layer of this RUN's first attention; state_base: its offset in the slot's state"""
+        ops, T = ctx.ops, x.shape[0]
+        n = ops.empty((T, self.W))
+        ops.norm_rows(x, self.w["norm1"], ctx.eps, n)
+        D = ops.linear(n, self.w["in"])
+        cat = ops.empty((T, self.n_out))
+        a = c = 0
+        for _, part, scale in self.parts:
+            part.forward(ctx, D[:, a:a + part.n_in], cat[:, c:c + part.n_out], kv_base, state_base, scale)
+            a, c = a + part.n_in, c + part.n_out
+            kv_base += 1 if part.kv_dim else 0
+            state_base += part.state_floats
+        ops.linear(cat, self.w["out"], out=x, add=True)
 
 
 def assign_cache_layers(layers: List[PostNormLayer]) -> int:

@@ -15,7 +15,7 @@ import torch
 
 from .. import _native as N
 
-EPI_NONE, EPI_RELU2, EPI_SOFTCAP = 0, 1, 2
+EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_ADD = 0, 1, 2, 3
 SM_COUNT = 148
 TC_MIN_ROWS = 128     # from this many rows on, a product of the bf16 serving mode runs on the tcgen05 GEMM
 WT_F32 = 3            # gemm_wt output mode: fp32 rows
@@ -30,6 +30,7 @@ class LayerOps:
         self.device, self.stream, self.exact = torch.device(device), stream, bool(exact)
         self.launches = 0
         self._inv_freq = {}
+        self._unit_seqs = {}
         self._on_stream = False
         self.tc_enabled = True
 
@@ -183,11 +184,13 @@ class LayerOps:
         return out
 
     def tc_gemm(self, Xb: torch.Tensor, W: torch.Tensor, Y: torch.Tensor, *, N_: int, K: int, ldw: Optional[int] = None,
-                ldy: Optional[int] = None, bias=None, rows: Optional[int] = None):
-        """Y[rows, N_] (fp32) = Xb[rows, ceil64(K)] (bf16) . W[N_, K]^T (bf16, row pitch ldw) on tcgen05"""
+                ldy: Optional[int] = None, bias=None, rows: Optional[int] = None, res: Optional[torch.Tensor] = None):
+        """Y[rows, N_] (fp32) = Xb[rows, ceil64(K)] (bf16) . W[N_, K]^T (bf16, row pitch ldw) (+ res, which may be Y
+        itself: a stream that accumulates in place) on tcgen05"""
         rows = Xb.shape[0] if rows is None else rows
         self._ok(self.lib.b200_gemm_wt_f32(Xb.data_ptr(), Xb.stride(0), W.data_ptr(), K if ldw is None else ldw,
-                                           N.ptr(bias), 0, 0, Y.data_ptr(), Y.stride(0) if ldy is None else ldy, 0, 0, 0,
+                                           N.ptr(bias), N.ptr(res), res.stride(0) if res is not None else 0,
+                                           Y.data_ptr(), Y.stride(0) if ldy is None else ldy, 0, 0, 0,
                                            rows, N_, K, 1, 0, WT_F32, self.s), "gemm_wt_f32")
 
     def moe_order(self, lists: torch.Tensor, count: torch.Tensor) -> torch.Tensor:
@@ -236,17 +239,97 @@ class LayerOps:
                  "lm_cache_transpose")
         return out
 
-    def linear(self, X: torch.Tensor, W: torch.Tensor, bias=None, epi=EPI_NONE, epi_param=0.0) -> torch.Tensor:
+    def linear(self, X: torch.Tensor, W: torch.Tensor, bias=None, epi=EPI_NONE, epi_param=0.0,
+               out: Optional[torch.Tensor] = None, add: bool = False) -> torch.Tensor:
+        """Y = epi(X . W^T + bias).  X and W may be column ranges of wider rows (their row pitch is taken from the
+        tensors).  out: the rows to write (else fresh ones); add: the product is added to what `out` holds."""
         (T, K), n = X.shape, W.shape[0]
-        Y = self.empty((T, n))
-        if epi == EPI_NONE and self.tc_ok(T, K):
+        Y = self.empty((T, n)) if out is None else out
+        ldw = W.stride(0) if n > 1 else K
+        if add:
+            assert out is not None and epi == EPI_NONE, "linear: adding needs the rows to add to and no other epilogue"
+        if epi == EPI_NONE and self.tc_ok(T, K, ldw) and W.data_ptr() % 16 == 0:
             try:
-                self.tc_gemm(self.to_bf16(X, K), W, Y, N_=n, K=K, bias=bias)
+                self.tc_gemm(self.to_bf16(X, K), W, Y, N_=n, K=K, ldw=ldw, bias=bias, res=Y if add else None)
                 return Y
             except N.B200Error as e:
                 self.tc_refused(e)
-        self.gemm(X, W, Y, M=T, N_=n, K=K, bias=bias, epi=epi, epi_param=epi_param)
+        self.gemm(X, W, Y, M=T, N_=n, K=K, ldw=ldw, bias=bias, epi=EPI_ADD if add else epi, epi_param=epi_param)
         return Y
+
+    # ---- sequences of a step, and the mixers that carry a state along them (csrc/mixer_ops.cu) -------------------
+    def seq_tables(self, segments, T: int):
+        """-> (first (T,), seqs (G, 2), G) on the device.  segments: (first row, rows, slot, first position) per
+        sequence of the step, or None: every row is a sequence of its own (a decode step; tables made once per T)"""
+        if segments is None:
+            if T not in self._unit_seqs:
+                idx = np.arange(T, dtype=np.int32)
+                both = self.to_device(np.concatenate([idx, np.stack([idx, np.ones(T, np.int32)], 1).reshape(-1)]))
+                self._unit_seqs[T] = (both[:T], both[T:].view(T, 2), T)
+            return self._unit_seqs[T]
+        first = np.empty(T, dtype=np.int32)
+        seqs = np.empty((len(segments), 2), dtype=np.int32)
+        for g, (start, n, _, _) in enumerate(segments):
+            first[start:start + n] = start
+            seqs[g] = (start, n)
+        both = self.to_device(np.concatenate([first, seqs.reshape(-1)]))
+        return both[:T], both[T:].view(len(segments), 2), len(segments)
+
+    def short_conv(self, U: torch.Tensor, w: torch.Tensor, state: torch.Tensor, ctx, act: bool = False) -> torch.Tensor:
+        """U (T, C) column range of projected rows; w (C, taps); state (slots, >= (taps-1) * C) fp32 view of the pool"""
+        T, C = U.shape
+        first, seqs, G = ctx.seq_tables()
+        Y = self.empty((T, C))
+        self._ok(self.lib.b200_lm_short_conv(U.data_ptr(), U.stride(0), w.data_ptr(), Y.data_ptr(), Y.stride(0),
+                                             state.data_ptr(), state.stride(0), ctx.slot.data_ptr(), ctx.pos.data_ptr(),
+                                             first.data_ptr(), seqs.data_ptr(), G, C, w.shape[1], int(act), T, self.s),
+                 "lm_short_conv")
+        return Y
+
+    def qkv_post(self, Q, K, V, cache_layer, slot, pos, cs, H, G, dim, vdim, rot_dims):
+        """Q rotated in place; cache_layer (slots, capacity, >= G * (dim + vdim)) gets the rotated K and V of the rows"""
+        self._ok(self.lib.b200_lm_qkv_post(Q.data_ptr(), Q.stride(0), K.data_ptr(), K.stride(0), V.data_ptr(), V.stride(0),
+                                           cache_layer.data_ptr(), int(cache_layer.dtype == torch.bfloat16),
+                                           cache_layer.stride(0), cache_layer.stride(1), slot.data_ptr(), pos.data_ptr(),
+                                           cs.data_ptr(), H, G, dim, vdim, rot_dims, Q.shape[0], self.s), "lm_qkv_post")
+
+    def sink_attention(self, Q, cache_layer, slot, pos, out, sink, H, G, dim, vdim, scale, chunk=0, window=0,
+                       n_split=None):
+        """n_split None: enough blocks per (token, kv head) to fill the GPU when the step has few tokens, 1 for prompts"""
+        T = Q.shape[0]
+        if n_split is None:
+            rep = H // G
+            groups = T * G * ((rep + 7) // 8)
+            n_split = max(1, min(64, (2 * SM_COUNT) // groups))
+        part = self.empty((T, H, n_split, vdim + 2)) if n_split > 1 else None
+        self._ok(self.lib.b200_lm_sink_attention(
+            Q.data_ptr(), Q.stride(0), cache_layer.data_ptr(), int(cache_layer.dtype == torch.bfloat16),
+            cache_layer.stride(0), cache_layer.stride(1), slot.data_ptr(), pos.data_ptr(), out.data_ptr(), out.stride(0),
+            N.ptr(sink), H, G, dim, vdim, float(scale), int(chunk), int(window), N.ptr(part), n_split, T, self.s),
+            "lm_sink_attention")
+
+    def linear_state(self, q, k, v, out, state, ctx, *, H, rep, dim, vdim, act=False, unit_eps=0.0, q_scale=1.0,
+                     decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False):
+        _, seqs, G = ctx.seq_tables()
+        self._ok(self.lib.b200_lm_linear_state(
+            q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
+            state.data_ptr(), state.stride(0), seqs.data_ptr(), G, ctx.slot.data_ptr(), ctx.pos.data_ptr(), H, rep, dim,
+            vdim, int(act), float(unit_eps), float(q_scale), N.ptr(decay_const), N.ptr(a), a.stride(0) if a is not None else 0,
+            N.ptr(A_log), N.ptr(dt_bias), N.ptr(b), b.stride(0) if b is not None else 0, int(delta), self.s),
+            "lm_linear_state")
+
+    def head_post(self, o, out, *, dv, gate=None, gate_per_head=False, gate_silu=False, w=None, eps=0.0, span=0,
+                  scale=1.0):
+        T, n = o.shape
+        self._ok(self.lib.b200_lm_head_post(o.data_ptr(), o.stride(0), N.ptr(gate), gate.stride(0) if gate is not None else 0,
+                                            N.ptr(w), w.numel() if w is not None else 0, float(eps), int(span),
+                                            int(gate_per_head), int(gate_silu), dv, n, float(scale), out.data_ptr(),
+                                            out.stride(0), T, self.s), "lm_head_post")
+
+    def glu_clamp(self, G, U, limit, alpha, Y):
+        T, n = G.shape
+        self._ok(self.lib.b200_lm_glu_clamp(G.data_ptr(), G.stride(0), U.data_ptr(), U.stride(0), float(limit),
+                                            float(alpha), Y.data_ptr(), Y.stride(0), n, T, self.s), "lm_glu_clamp")
 
     def argmax_rows(self, z, tok, logprob=None):
         B, V = z.shape

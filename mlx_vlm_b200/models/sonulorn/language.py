@@ -1,0 +1,43 @@
+"""Sonulorn language model: the call surface of the layer-assembled decoders (`step`, `__call__`, `make_cache`,
+`make_cache_row`, `make_pool`, `fused_greedy_decode_n`, `prefill_rows`: models/buzopel/language.py) over a
+`StatePool`: a request's slot holds the attention rows of every layer run that has an attention and one span of fp32
+state per recurrent layer run; a layer of the repeated span has its own rows and state in every repetition."""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..buzopel.language import LanguageModel as _LayeredLanguageModel
+from ..cache import RunCache, StatePool
+
+
+class LanguageModel(_LayeredLanguageModel):
+    def __init__(self, args, core, engine_getter):
+        super().__init__(args, core, engine_getter)
+        self.model_type = "sonulorn"
+
+    @property
+    def layers(self):
+        return list(range(len(self.core.runs)))
+
+    def make_pool(self, rows: int = 1, capacity: int = 0) -> StatePool:
+        eng = self._engine()
+        with torch.cuda.stream(eng.stream):
+            return StatePool(self.core.n_cache_layers, self.core.row_dim, self.core.state_floats, eng.device, batch=rows,
+                             capacity=capacity, dtype=eng.ops.cache_dtype)
+
+    def make_cache_row(self, pool: StatePool, row: int) -> List[RunCache]:
+        out = []
+        for run in self.core.runs:
+            L = self.core.layers[run.layer]
+            out.append(RunCache(pool, row, kv_layer=run.kv_base if L.kv_layers else None, kv_dim=L.kv_dim,
+                                state_off=run.state_base, state_len=L.state_floats))
+        return out
+
+    def make_cache(self) -> List[RunCache]:
+        return self.make_cache_row(self.make_pool(1), 0)
+
+    @property
+    def head_dim(self) -> int:
+        return self.core.row_dim
