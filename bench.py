@@ -511,8 +511,9 @@ def c4_leg(dev, args):
 
 
 # ------------------------------------------------------------------------------------------------------------
-# `--design buzopel`: prefill and decode throughput of the Buzopel design (latent attention + expert mixture,
-# assembled from decoder_blocks over the layer ops) at sizes that resemble real layers, beside the closest
+# `--design buzopel | sonulorn`: prefill and decode throughput of a decoder design assembled from decoder_blocks
+# over the layer ops (Buzopel: latent attention + expert mixture; Sonulorn: sink attention, matrix-state mixers and a
+# clamped gated feed-forward behind one shared input projection) at sizes that resemble real layers, beside the closest
 # existing model of the package — the Qwen2-VL language model (dense GQA decoder on the native engine) — at equal
 # width, depth, head count and ACTIVE feed-forward size.  Random weights; inputs are token ids resident on the host;
 # CUDA events on the engine's stream; the weights of either model (>= 1 GB) exceed the L2.
@@ -536,14 +537,78 @@ def _buzopel_config(z):
             "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "logit_softcap": 30.0}
 
 
+def _sonulorn_config(z):
+    H, G, d = z["heads"], z["kv_heads"], z["dim"]
+    att = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "rot": {"base": 1000000.0, "dims": d // 2}, "scale": d ** -0.5}
+    mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    left = dict(att, conv=3)
+    right = {"heads": H, "kv_heads": max(1, H // 2), "dim": d, "vdim": d, "conv": 4}
+    layers = [{"type": "parallel", "mixer": {"left": left, "left_scale": 0.7, "right": right, "right_scale": 0.7}, "mlp": mlp},
+              {"type": "lightning", "mixer": {"heads": H, "dim": d, "vdim": d,
+                                              "decay": [1.0 - 2.0 ** -(3 + 5 * h / H) for h in range(H)]}, "mlp": mlp},
+              {"type": "attention", "mixer": dict(att, mask={"size": z["chunk"]}), "mlp": mlp},
+              {"type": "lightning", "mixer": {"heads": H, "dim": d, "vdim": d,
+                                              "decay": [1.0 - 2.0 ** -(3 + 5 * h / H) for h in range(H)]}, "mlp": mlp}]
+    return {"architecture": "Sonulorn", "vocab": z["vocab"], "width": z["width"], "layers": layers[:z["layers"]],
+            "loop": {"start": 0, "stop": z["layers"], "times": 1}, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}}
+
+
+SONULORN_SIZES = {
+    "2048w": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, chunk=1024, ff=8192, top=1, vocab=32000),
+    "4096w": dict(width=4096, layers=4, heads=32, kv_heads=8, dim=128, chunk=1024, ff=14336, top=1, vocab=32000),
+}
+
+
+def _buzopel_model(z, dev):
+    from mlx_vlm_b200.models.buzopel import Model as BModel, ModelConfig as BConfig
+    return BModel(BConfig.from_dict(_buzopel_config(z)), device=dev).init_random(0)
+
+
+def _buzopel_account(m, z, T):
+    """(bf16 weight elements a decoded token touches, other bytes it moves, attention / mixer flops per prompt token)"""
+    act_w = sum((2 * L.mixer.q_rank * z["width"] + (L.mixer.row_dim * z["width"] if L.mixer.own_kv else 0)
+                 + L.mixer.H * (L.mixer.dim + L.mixer.rot_dim) * L.mixer.q_rank + L.mixer.H * L.mixer.dim * L.mixer.kv_rank
+                 + L.mixer.H * L.mixer.vdim * L.mixer.kv_rank + z["width"] * L.mixer.H * L.mixer.vdim
+                 + L.ff.E * z["width"] + 2 * L.ff.top * L.ff.ff * z["width"]) for L in m.layers) \
+        - sum(L.mixer.q_rank * z["width"] for L in m.layers)
+    att_flops = sum(2 * L.mixer.H * (L.mixer.row_dim + L.mixer.kv_rank) * (T / 2) for L in m.layers)
+    return act_w, 0, att_flops
+
+
+def _sonulorn_model(z, dev):
+    from mlx_vlm_b200.models.sonulorn import Model as SModel, ModelConfig as SConfig
+    return SModel(SConfig.from_dict(_sonulorn_config(z)), device=dev).init_random(0)
+
+
+def _sonulorn_account(m, z, T):
+    from mlx_vlm_b200.models.decoder_blocks import SinkAttention
+    W = z["width"]
+    act_w = sum((m.layers[r.layer].n_in + m.layers[r.layer].n_out) * W for r in m.runs) + 2 * W * W * len([r for r in m.runs if r.opens_pass])
+    other = 8 * m.state_floats           # the fp32 state is read and written once per token
+    mix_flops = 0.0
+    for r in m.runs:
+        for _, part, _ in m.layers[r.layer].parts:
+            if isinstance(part, SinkAttention):
+                seen = min(part.chunk, T) / 2 if part.chunk else T / 2
+                mix_flops += 2 * part.H * (part.dim + part.vdim) * seen
+                other += 2 * part.kv_dim * (T if not part.chunk else min(part.chunk, T) / 2)     # cached rows a decoded token reads
+            elif part.state_floats:
+                mix_flops += (6 if hasattr(part, "unit_eps") else 4) * part.H * part.dim * part.vdim
+    return act_w, other, mix_flops
+
+
+DESIGNS = {"buzopel": (DESIGN_SIZES, _buzopel_model, _buzopel_account),
+           "sonulorn": (SONULORN_SIZES, _sonulorn_model, _sonulorn_account)}
+
+
 def design_leg(dev, args):
     import numpy as np
     import torch
-    from mlx_vlm_b200.models.buzopel import Model as BModel, ModelConfig as BConfig
     from mlx_vlm_b200.models.cache import make_prompt_cache
     from mlx_vlm_b200.models.qwen2_vl.config import ModelConfig as QConfig, TextConfig, VisionConfig
     from mlx_vlm_b200.utils import load_synthetic
     T, n_dec, rows = args.design_prompt, args.design_out, args.design_rows
+    sizes, make_model, account = DESIGNS[args.design]
     hbm, hbm_src = _peaks()
     tpk, tpk_src = _tensor_peak()
     out = {"prompt_tokens": T, "decode_tokens": n_dec, "rows": rows, "sizes": {}, "peaks": {"hbm_GBs": hbm, "hbm_source": hbm_src,
@@ -562,13 +627,13 @@ def design_leg(dev, args):
         eng.stream.synchronize()
         return ev[0].elapsed_time(ev[1]) / args.steps
 
-    for name, z in DESIGN_SIZES.items():
+    for name, z in sizes.items():
         if args.design_sizes and name not in args.design_sizes.split(","):
             continue
         ids = rng.integers(0, z["vocab"], size=(1, T))
         res = {}
         # ---- the new design ------------------------------------------------------------------------------
-        m = BModel(BConfig.from_dict(_buzopel_config(z)), device=dev).init_random(0)
+        m = make_model(z, dev)
         lm, eng = m.language_model, m.engine
         state = {}
 
@@ -587,22 +652,16 @@ def design_leg(dev, args):
         eng.bind_pool(pool)
         eng.batch_begin([1] * rows, [T] * rows, [T] * rows, [1] * rows)
         bdec = timed(eng, lambda: eng.batch_decode(n_dec)) / n_dec
-        mx, ff = m.layers[0].mixer, m.layers[0].ff
-        act_w = sum((2 * L.mixer.q_rank * z["width"] + (L.mixer.row_dim * z["width"] if L.mixer.own_kv else 0)
-                     + L.mixer.H * (L.mixer.dim + L.mixer.rot_dim) * L.mixer.q_rank + L.mixer.H * L.mixer.dim * L.mixer.kv_rank
-                     + L.mixer.H * L.mixer.vdim * L.mixer.kv_rank + z["width"] * L.mixer.H * L.mixer.vdim
-                     + L.ff.E * z["width"] + 2 * L.ff.top * L.ff.ff * z["width"]) for L in m.layers) \
-            - sum(L.mixer.q_rank * z["width"] for L in m.layers)
+        act_w, other_bytes, att_flops = account(m, z, T)
         head_w = z["vocab"] * z["width"]
-        bytes_tok = 2 * (act_w + head_w)                                   # bf16 weights one decoded token touches
+        bytes_tok = 2 * (act_w + head_w) + other_bytes                     # what one decoded token has to move
         flops_tok = 2 * (act_w + head_w / T)                               # prefill: the head runs on one row
-        att_flops = sum(2 * L.mixer.H * (L.mixer.row_dim + L.mixer.kv_rank) * (T / 2) for L in m.layers)
-        res["buzopel"] = {"prefill_ms": pre, "prefill_tok_s": T / pre * 1e3, "decode_ms_per_token": dec,
-                          "decode_tok_s": 1e3 / dec, "batch_decode_ms_per_step": bdec, "batch_decode_tok_s": rows / bdec * 1e3,
-                          "active_weight_bytes_per_token": bytes_tok,
-                          "decode_frac_of_hbm": bytes_tok / (dec / 1e3) / 1e9 / hbm,
-                          "prefill_frac_of_tensor": (flops_tok + att_flops) * T / (pre / 1e3) / 1e12 / tpk,
-                          "graph_replays": eng.graph_replays, "launches": eng.launch_count}
+        res[args.design] = {"prefill_ms": pre, "prefill_tok_s": T / pre * 1e3, "decode_ms_per_token": dec,
+                            "decode_tok_s": 1e3 / dec, "batch_decode_ms_per_step": bdec, "batch_decode_tok_s": rows / bdec * 1e3,
+                            "active_weight_bytes_per_token": 2 * (act_w + head_w), "bytes_per_decoded_token": bytes_tok,
+                            "decode_frac_of_hbm": bytes_tok / (dec / 1e3) / 1e9 / hbm,
+                            "prefill_frac_of_tensor": (flops_tok + att_flops) * T / (pre / 1e3) / 1e12 / tpk,
+                            "graph_replays": eng.graph_replays, "launches": eng.launch_count}
         del m, lm, eng, pool, caches
         state.clear()
         torch.cuda.empty_cache()
@@ -663,7 +722,7 @@ def main():
     ap.add_argument("--no-mega", action="store_true")
     ap.add_argument("--mega-mode", type=int, default=None,
                     help="decode kernel: 0 per-phase kernels, 1 k_mega (CUDA cores), 2 k_mega_tc (tcgen05)")
-    ap.add_argument("--design", default=None, choices=["buzopel"],
+    ap.add_argument("--design", default=None, choices=["buzopel", "sonulorn"],
                     help="instead of the default workload: prefill / decode throughput of this decoder design at "
                          "layer sizes of real models, beside the closest existing model at equal size")
     ap.add_argument("--design-sizes", default="", help="comma-separated subset of the sizes (default: all)")

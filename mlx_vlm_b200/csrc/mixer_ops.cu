@@ -353,19 +353,26 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       const float d = dec[tk];
       float u = vs[tk][cj];
       if (p.delta) {
-        float dot = 0.f;
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;     // four running sums over i mod 4: short dependency chains
 #pragma unroll
-        for (int i = 0; i < 32; ++i) dot = fmaf(S[i], kr[i], dot);
+        for (int i = 0; i < 32; i += 4) {
+          d0 = fmaf(S[i], kr[i], d0); d1 = fmaf(S[i + 1], kr[i + 1], d1);
+          d2 = fmaf(S[i + 2], kr[i + 2], d2); d3 = fmaf(S[i + 3], kr[i + 3], d3);
+        }
+        float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
         for (int o = 1; o < P; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         u = bet[tk] * (u - d * dot);
       }
-      float o_ = 0.f;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        S[i] = fmaf(kr[i], u, d * S[i]);
-        o_ = fmaf(S[i], qr[i], o_);
+      for (int i = 0; i < 32; i += 4) {
+        S[i] = fmaf(kr[i], u, d * S[i]);             o0 = fmaf(S[i], qr[i], o0);
+        S[i + 1] = fmaf(kr[i + 1], u, d * S[i + 1]); o1 = fmaf(S[i + 1], qr[i + 1], o1);
+        S[i + 2] = fmaf(kr[i + 2], u, d * S[i + 2]); o2 = fmaf(S[i + 2], qr[i + 2], o2);
+        S[i + 3] = fmaf(kr[i + 3], u, d * S[i + 3]); o3 = fmaf(S[i + 3], qr[i + 3], o3);
       }
+      float o_ = (o0 + o1) + (o2 + o3);
 #pragma unroll
       for (int o = 1; o < P; o <<= 1) o_ += __shfl_xor_sync(0xffffffffu, o_, o);
       if (r == 0 && valid) p.out[(long)(start + c0 + tk) * p.ldo + (long)h * p.vdim + col] = o_;
@@ -425,6 +432,55 @@ __global__ void glu_clamp_kernel(const float* __restrict__ G, long ldg, const fl
     const float u = fminf(fmaxf(U[(long)t * ldu + i], -lim), lim);
     Y[(long)t * ldy + i] = g * sigmoid_exact(alpha * g) * (u + 1.0f);
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Operands of the tensor-core attention of a prompt step (bf16 serving mode; the two products are the weight-major
+// tcgen05 GEMM with fp32 output): the `rep` query heads that share a key/value head as bf16 rows (t, r), padded with
+// zeros to Kp columns; and the softmax of their score rows against the keys at positions key0 .. key0 + n_keys - 1 —
+// visible: max(start of pos's block, pos - window + 1, key0) .. pos — with the sink logit of the row's head in the
+// denominator, written as bf16 probabilities (normalised in fp32 before the rounding), zero where nothing is seen
+__global__ void heads_to_bf16_kernel(const float* __restrict__ q, long ldq, int rep, int dim, bf16* __restrict__ out,
+                                     int Kp) {
+  const int i = blockIdx.x, t = i / rep, r = i % rep;
+  const float* x = q + (long)t * ldq + r * dim;
+  for (int k = threadIdx.x; k < Kp; k += blockDim.x) out[(long)i * Kp + k] = f2bf(k < dim ? x[k] : 0.f);
+}
+__device__ __forceinline__ float block_sum_fixed(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+__global__ void sink_softmax_bf16_kernel(const float* __restrict__ S, long lds, const int* __restrict__ pos, int rep,
+                                         const bf16* __restrict__ sink, float scale, int chunk, int window, int key0,
+                                         bf16* __restrict__ P, long ldp, int Sp) {
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  const int ps = pos[r / rep];
+  int lo = key0;
+  if (chunk > 0) lo = max(lo, (ps / chunk) * chunk);
+  if (window > 0) lo = max(lo, ps - window + 1);
+  const int j0 = lo - key0, j1 = ps - key0;            // visible columns j0 .. j1
+  const float* s = S + r * lds;
+  const float sk = sink ? bf2f(sink[r % rep]) : -INFINITY;
+  float m = sk;
+  for (int j = j0 + threadIdx.x; j <= j1; j += blockDim.x) m = fmaxf(m, s[j] * scale);
+  m = warp_max(m);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, red[i]);
+  float sum = 0.f;
+  for (int j = j0 + threadIdx.x; j <= j1; j += blockDim.x) sum += expf(s[j] * scale - m);
+  const float tot = block_sum_fixed(sum, red) + (sink ? expf(sk - m) : 0.f);
+  const float inv = 1.0f / tot;
+  for (int j = threadIdx.x; j < Sp; j += blockDim.x)
+    P[r * ldp + j] = f2bf((j >= j0 && j <= j1) ? expf(s[j] * scale - m) * inv : 0.f);
 }
 
 unsigned long long g_sink_attr_f32 = 0, g_sink_attr_bf16 = 0;
@@ -516,6 +572,22 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
   else if (dim <= 64) linear_state_kernel<2><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 2)), LS_THREADS, 0, cs>>>(p);
   else if (dim <= 128) linear_state_kernel<4><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 4)), LS_THREADS, 0, cs>>>(p);
   else linear_state_kernel<8><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 8)), LS_THREADS, 0, cs>>>(p);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_heads_to_bf16(const float* q, long ldq, int rep, int dim, void* out, int Kp, int T, void* st) {
+  B200_REQUIRE(q && out && T > 0 && rep > 0 && dim > 0 && Kp >= dim, "lm_heads_to_bf16: bad argument");
+  heads_to_bf16_kernel<<<T * rep, 128, 0, (cudaStream_t)st>>>(q, ldq, rep, dim, (bf16*)out, Kp);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_sink_softmax_bf16(const float* S, long lds, const int* pos, int rep, const void* sink, float scale, int chunk,
+                              int window, int key0, void* P, long ldp, int rows, int Sp, void* st) {
+  B200_REQUIRE(S && pos && P && rows > 0 && rep > 0 && Sp > 0 && key0 >= 0, "lm_sink_softmax_bf16: bad argument");
+  sink_softmax_bf16_kernel<<<rows, 256, 0, (cudaStream_t)st>>>(S, lds, pos, rep, (const bf16*)sink, scale, chunk, window,
+                                                                key0, (bf16*)P, ldp, Sp);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

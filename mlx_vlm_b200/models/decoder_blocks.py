@@ -355,9 +355,68 @@ class SinkAttention:
         ops.qkv_post(q, k, v, rows, ctx.slot, ctx.pos, ctx.rope(self.rot_base, self.rot_dims), self.H, self.G, self.dim,
                      self.vdim, self.rot_dims)
         o = ops.empty((T, self.n_out))
-        ops.sink_attention(q, rows, ctx.slot, ctx.pos, o, w["sink"], self.H, self.G, self.dim, self.vdim, self.scale,
-                           chunk=self.chunk, window=self.window, n_split=1 if ctx.segments is not None and T > 16 else None)
+        segs = ctx.segments or []
+        done = False
+        if rows.dtype == torch.bfloat16 and not self.window and any(self._tc_portion(ops, n, rows) for _, n, _, _ in segs):
+            try:
+                for start, n, slot, p0 in segs:      # long portions on the tensor cores, the rest on the row kernel
+                    sl = slice(start, start + n)
+                    if self._tc_portion(ops, n, rows):
+                        self._attend_prompt(ctx, q[sl], rows, slot, ctx.slot[sl], ctx.pos[sl], o[sl], p0, n)
+                    else:
+                        self._attend_rows(ctx, q[sl], rows, ctx.slot[sl], ctx.pos[sl], o[sl], prompt=True)
+                done = True
+            except _B200Error as e:
+                ops.tc_refused(e)
+        if not done:
+            self._attend_rows(ctx, q, rows, ctx.slot, ctx.pos, o, prompt=ctx.segments is not None)
         ops.head_post(o, cat, dv=self.vdim, gate=D[:, nq + nk + nv:], gate_per_head=self.gate == "head", scale=out_scale)
+
+    def _tc_portion(self, ops: LayerOps, n: int, rows) -> bool:
+        return ops.tc_ok(n, self.dim, rows.stride(1)) and rows.stride(0) % 8 == 0
+
+    def _attend_rows(self, ctx: StepCtx, q, rows, slot, pos, o, prompt: bool):
+        """the row kernel: every query finds its keys by (slot, position); a step of few tokens (decoding) spreads the
+        keys of a query over several blocks"""
+        ctx.ops.sink_attention(q, rows, slot, pos, o, self.w["sink"], self.H, self.G, self.dim, self.vdim, self.scale,
+                               chunk=self.chunk, window=self.window, n_split=1 if prompt and q.shape[0] > 16 else None)
+
+    def _attend_prompt(self, ctx: StepCtx, q, all_rows, slot_index: int, slot, pos, o, p0: int, n: int):
+        """A portion of a prompt (positions p0 .. p0 + n - 1 of one slot) as two tcgen05 products per key/value head:
+        the cached key columns of that head are the weight-major operand of the scores of the query heads that share
+        it, an fp32 softmax over the visible keys (with the sink logit in the denominator) writes bf16 probabilities,
+        and the head's value columns, transposed, are the operand of the weighted sum.  With block-local keys the
+        portion is taken block by block, each against the keys of its own block only.  Queries are taken in chunks
+        that bound the score buffer; a block's share of fewer rows than a tile goes to the row kernel."""
+        ops, H, G, d, dv = ctx.ops, self.H, self.G, self.dim, self.vdim
+        rep, rows = H // G, all_rows[slot_index]
+        if self.chunk:
+            spans = [(max(p0, b * self.chunk), min(p0 + n, (b + 1) * self.chunk), b * self.chunk)
+                     for b in range(p0 // self.chunk, (p0 + n - 1) // self.chunk + 1)]
+        else:
+            spans = [(p0, p0 + n, 0)]
+        for qa, qb, key0 in spans:
+            m, a0 = qb - qa, qa - p0
+            if not ops.tc_ok(m, d):
+                sl = slice(a0, a0 + m)
+                self._attend_rows(ctx, q[sl], all_rows, slot[sl], pos[sl], o[sl], prompt=True)
+                continue
+            S = qb - key0
+            Sp = (S + 63) // 64 * 64
+            step = max(1, min(m, (1 << 27) // (rep * Sp)))
+            for g in range(G):
+                keys = rows[key0:key0 + S, g * d:(g + 1) * d]
+                vt = ops.cache_transpose(rows[key0:, G * d + g * dv:], S, Sp, dv)
+                for a in range(a0, a0 + m, step):
+                    mm = min(step, a0 + m - a)
+                    qb16 = ops.heads_to_bf16(q[a:a + mm, g * rep * d:], rep, d)
+                    sc = ops.empty((mm * rep, S))
+                    ops.tc_gemm(qb16, keys, sc, N_=S, K=d, ldw=rows.stride(0))
+                    P = ops.empty((mm * rep, Sp), torch.bfloat16)
+                    ops.sink_softmax_bf16(sc, pos[a:a + mm], rep, self.w["sink"][g * rep:], self.scale, self.chunk, 0, key0, P)
+                    og = ops.empty((mm * rep, dv))
+                    ops.tc_gemm(P, vt, og, N_=dv, K=Sp)
+                    ops.head_post(og.view(mm, rep * dv), o[a:a + mm, g * rep * dv:(g + 1) * rep * dv], dv=dv)
 
 
 def state_lanes(dim: int) -> int:

@@ -308,6 +308,19 @@ class LayerOps:
             N.ptr(sink), H, G, dim, vdim, float(scale), int(chunk), int(window), N.ptr(part), n_split, T, self.s),
             "lm_sink_attention")
 
+    def heads_to_bf16(self, q: torch.Tensor, rep: int, dim: int) -> torch.Tensor:
+        """q (n, >= rep * dim) fp32 columns of `rep` heads -> bf16 rows (n * rep, ceil64(dim))"""
+        n, Kp = q.shape[0], (dim + 63) // 64 * 64
+        out = self.empty((n * rep, Kp), torch.bfloat16)
+        self._ok(self.lib.b200_lm_heads_to_bf16(q.data_ptr(), q.stride(0), rep, dim, out.data_ptr(), Kp, n, self.s),
+                 "lm_heads_to_bf16")
+        return out
+
+    def sink_softmax_bf16(self, S, pos, rep, sink, scale, chunk, window, key0, P):
+        self._ok(self.lib.b200_lm_sink_softmax_bf16(S.data_ptr(), S.stride(0), pos.data_ptr(), rep, N.ptr(sink), float(scale),
+                                                    int(chunk), int(window), int(key0), P.data_ptr(), P.stride(0),
+                                                    S.shape[0], P.shape[1], self.s), "lm_sink_softmax_bf16")
+
     def linear_state(self, q, k, v, out, state, ctx, *, H, rep, dim, vdim, act=False, unit_eps=0.0, q_scale=1.0,
                      decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False):
         _, seqs, G = ctx.seq_tables()

@@ -491,6 +491,13 @@ def test_long_prompt_paths_of_the_serving_mode():
     ref = O.forward(cfg, W, toks)
     assert rel(run_alone(model, toks, [140, 150, 40]), ref) < TOL["bfloat16"]
     assert rel(run_alone(exact, toks, [140, 150, 40]), ref) < TOL["float32"]
+    # blocks of visible keys as long as a tile: a block's share of a portion runs against that block's keys only
+    wide = config([L_attn(block=150, heads=6, kv_heads=2), L_par(left=attn(heads=4, kv_heads=2, dim=16, vdim=8, rot=16, conv=3, block=200))],
+                  loop=(0, 2, 2))
+    m2, W2 = build(wide, "bfloat16", seed=6)
+    ref2 = O.forward(wide, W2, toks)
+    assert rel(run_alone(m2, toks, [140, 150, 40]), ref2) < TOL["bfloat16"]
+    assert rel(run_alone(m2, toks), ref2) < TOL["bfloat16"]
     pool = lm.make_pool(2, 512)
     ca, cb = lm.make_cache_row(pool, 0), lm.make_cache_row(pool, 1)
     both = host(eng, lm.step([toks[:200], toks[:30]], [ca, cb], want=[list(range(200)), list(range(30))]))
