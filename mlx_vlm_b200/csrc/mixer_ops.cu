@@ -270,7 +270,7 @@ __global__ void sink_attention_merge_kernel(const float* __restrict__ part, int 
 // The slot keeps S between steps as [H][32][vdim][P] (row r * 32 + i of column c at ((h * 32 + i) * vdim + c) * P + r),
 // which makes the loads and stores of a warp contiguous; a sequence that starts at position 0 starts from zero.
 // q and k may be shared by `rep` heads, passed through silu, and scaled to unit length per head at load.
-constexpr int LS_CT = 16, LS_THREADS = 128;
+constexpr int LS_CT = 16, LS_THREADS = 128;   // LS_CT * 32 P must be a multiple of LS_THREADS
 struct StateP {
   const float* q; long ldq;
   const float* k; long ldk;
@@ -290,10 +290,15 @@ struct StateP {
 };
 template <int P>
 __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
-  constexpr int CB = LS_THREADS / P, LD = P * 33;
-  __shared__ float ks[LS_CT][LD], qs[LS_CT][LD];
+  // Tokens are staged LS_CT at a time.  The raw q, k, v, decay and beta inputs of the NEXT group are requested from
+  // global memory into registers before the current group is walked, so their latency hides behind the walk.
+  // Per token, with S the state before it:  dk = S^T k, dq = S^T q (one pass, one butterfly for both),
+  // u = beta (v - decay dk) (or v),  o = decay dq + u (k . q),  S <- decay S + k u^T  — o does not wait for the update.
+  constexpr int CB = LS_THREADS / P, RS = 36, LD = P * RS, DKP = P * 32;
+  constexpr int NQK = LS_CT * DKP / LS_THREADS, NV = (LS_CT * CB + LS_THREADS - 1) / LS_THREADS;
+  __shared__ __align__(16) float ks[LS_CT][LD], qs[LS_CT][LD];
   __shared__ float vs[LS_CT][CB];
-  __shared__ float dec[LS_CT], bet[LS_CT];
+  __shared__ float dec[LS_CT], bet[LS_CT], kq[LS_CT];
   const int start = p.seqs[2 * blockIdx.x], rows = p.seqs[2 * blockIdx.x + 1];
   const int h = blockIdx.y, hk = h / p.rep;
   const int cj = threadIdx.x / P, r = threadIdx.x % P, col = blockIdx.z * CB + cj;
@@ -308,74 +313,98 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) S[i] = 0.f;
   }
-  for (int e = threadIdx.x; e < LS_CT * LD; e += LS_THREADS) { (&ks[0][0])[e] = 0.f; (&qs[0][0])[e] = 0.f; }
+  float rk[NQK], rq[NQK], rv[NV], ra = 0.f, rb = 0.f;
+  auto request = [&](int c0) {               // raw inputs of tokens c0 .. c0 + LS_CT - 1 (zeros past the end)
+    const int nc = min(LS_CT, rows - c0);
+#pragma unroll
+    for (int n = 0; n < NQK; ++n) {
+      const int e = threadIdx.x + n * LS_THREADS, tk = e / DKP, i = e % DKP;
+      const bool ok = tk < nc && i < p.dim;
+      const long t = start + c0 + tk;
+      rk[n] = ok ? p.k[t * p.ldk + (long)hk * p.dim + i] : 0.f;
+      rq[n] = ok ? p.q[t * p.ldq + (long)hk * p.dim + i] : 0.f;
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int e = threadIdx.x + n * LS_THREADS, tk = e / CB, cc = blockIdx.z * CB + e % CB;
+      rv[n] = (tk < nc && cc < p.vdim) ? p.v[(long)(start + c0 + tk) * p.ldv + (long)h * p.vdim + cc] : 0.f;
+    }
+    if ((int)threadIdx.x < nc) {
+      const long t = start + c0 + threadIdx.x;
+      if (!p.decay_const) ra = p.a[t * p.lda + h];
+      if (p.b) rb = p.b[t * p.ldb + h];
+    }
+  };
+  const float A = p.decay_const ? 0.f : expf(bf2f(p.A_log[h])), dtb = p.decay_const ? 0.f : bf2f(p.dt_bias[h]);
+  const float dconst = p.decay_const ? p.decay_const[h] : 0.f;
+  request(0);
   for (int c0 = 0; c0 < rows; c0 += LS_CT) {
     const int nc = min(LS_CT, rows - c0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nc * p.dim; e += LS_THREADS) {
-      const int tk = e / p.dim, i = e - tk * p.dim;
-      const long t = start + c0 + tk;
-      float kv = p.k[t * p.ldk + (long)hk * p.dim + i], qv = p.q[t * p.ldq + (long)hk * p.dim + i];
-      if (p.act) { kv = silu_exact(kv); qv = silu_exact(qv); }
-      ks[tk][(i >> 5) * 33 + (i & 31)] = kv;
-      qs[tk][(i >> 5) * 33 + (i & 31)] = qv;
+    __syncthreads();                          // the walk over the previous group is over
+#pragma unroll
+    for (int n = 0; n < NQK; ++n) {
+      const int e = threadIdx.x + n * LS_THREADS, tk = e / DKP, i = e % DKP;
+      ks[tk][(i >> 5) * RS + (i & 31)] = p.act ? silu_exact(rk[n]) : rk[n];
+      qs[tk][(i >> 5) * RS + (i & 31)] = p.act ? silu_exact(rq[n]) : rq[n];
     }
-    for (int e = threadIdx.x; e < nc * CB; e += LS_THREADS) {
-      const int tk = e / CB, c = e - tk * CB, cc = blockIdx.z * CB + c;
-      float vv = cc < p.vdim ? p.v[(long)(start + c0 + tk) * p.ldv + (long)h * p.vdim + cc] : 0.f;
-      vs[tk][c] = p.act ? silu_exact(vv) : vv;
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int e = threadIdx.x + n * LS_THREADS;
+      if (e < LS_CT * CB) vs[e / CB][e % CB] = p.act ? silu_exact(rv[n]) : rv[n];
     }
-    if (threadIdx.x < nc) {
-      const long t = start + c0 + threadIdx.x;
-      dec[threadIdx.x] = p.decay_const ? p.decay_const[h]
-          : expf(-expf(bf2f(p.A_log[h])) * softplus_exact(p.a[t * p.lda + h] + bf2f(p.dt_bias[h])));
-      bet[threadIdx.x] = p.b ? sigmoid_exact(p.b[t * p.ldb + h]) : 1.f;
+    if ((int)threadIdx.x < nc) {
+      dec[threadIdx.x] = p.decay_const ? dconst : expf(-A * softplus_exact(ra + dtb));
+      bet[threadIdx.x] = p.b ? sigmoid_exact(rb) : 1.f;
     }
     __syncthreads();
-    if (p.unit_eps > 0.f) {                   // a warp per token row: lengths in a fixed order, then the scaling
-      for (int tk = warp; tk < nc; tk += LS_THREADS / 32) {
+    for (int tk = warp; tk < nc; tk += LS_THREADS / 32) {      // a warp per token row: lengths and k . q in a fixed order
+      float ik = 1.f, iq = 1.f;
+      if (p.unit_eps > 0.f) {
         float sk = 0.f, sq = 0.f;
         for (int i = lane; i < p.dim; i += 32) {
-          const float a = ks[tk][(i >> 5) * 33 + (i & 31)], b = qs[tk][(i >> 5) * 33 + (i & 31)];
+          const float a = ks[tk][(i >> 5) * RS + (i & 31)], b = qs[tk][(i >> 5) * RS + (i & 31)];
           sk = fmaf(a, a, sk); sq = fmaf(b, b, sq);
         }
-        const float ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps), iq = p.q_scale / sqrtf(warp_sum(sq) + p.unit_eps);
-        for (int i = lane; i < p.dim; i += 32) {
-          ks[tk][(i >> 5) * 33 + (i & 31)] *= ik;
-          qs[tk][(i >> 5) * 33 + (i & 31)] *= iq;
-        }
+        ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps);
+        iq = p.q_scale / sqrtf(warp_sum(sq) + p.unit_eps);
       }
-      __syncthreads();
+      float dot = 0.f;
+      for (int i = lane; i < p.dim; i += 32) {
+        const int at = (i >> 5) * RS + (i & 31);
+        const float a = ks[tk][at] * ik, b = qs[tk][at] * iq;
+        ks[tk][at] = a; qs[tk][at] = b;
+        dot = fmaf(a, b, dot);
+      }
+      dot = warp_sum(dot);
+      if (lane == 0) kq[tk] = dot;
     }
+    __syncthreads();
+    if (c0 + LS_CT < rows) request(c0 + LS_CT);
     for (int tk = 0; tk < nc; ++tk) {
-      const float* kr = &ks[tk][r * 33];
-      const float* qr = &qs[tk][r * 33];
+      const float* kr = &ks[tk][r * RS];
+      const float* qr = &qs[tk][r * RS];
       const float d = dec[tk];
+      float k_[32];
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {          // four running sums per dot over i mod 4: short dependency chains
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
+        k_[i] = k4.x; k_[i + 1] = k4.y; k_[i + 2] = k4.z; k_[i + 3] = k4.w;
+        a0 = fmaf(S[i], k4.x, a0); a1 = fmaf(S[i + 1], k4.y, a1); a2 = fmaf(S[i + 2], k4.z, a2); a3 = fmaf(S[i + 3], k4.w, a3);
+        b0 = fmaf(S[i], q4.x, b0); b1 = fmaf(S[i + 1], q4.y, b1); b2 = fmaf(S[i + 2], q4.z, b2); b3 = fmaf(S[i + 3], q4.w, b3);
+      }
+      float dk = (a0 + a1) + (a2 + a3), dq = (b0 + b1) + (b2 + b3);
+#pragma unroll
+      for (int o = 1; o < P; o <<= 1) {
+        dk += __shfl_xor_sync(0xffffffffu, dk, o);
+        dq += __shfl_xor_sync(0xffffffffu, dq, o);
+      }
       float u = vs[tk][cj];
-      if (p.delta) {
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;     // four running sums over i mod 4: short dependency chains
+      if (p.delta) u = bet[tk] * (u - d * dk);
+      if (r == 0 && valid) p.out[(long)(start + c0 + tk) * p.ldo + (long)h * p.vdim + col] = fmaf(u, kq[tk], d * dq);
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          d0 = fmaf(S[i], kr[i], d0); d1 = fmaf(S[i + 1], kr[i + 1], d1);
-          d2 = fmaf(S[i + 2], kr[i + 2], d2); d3 = fmaf(S[i + 3], kr[i + 3], d3);
-        }
-        float dot = (d0 + d1) + (d2 + d3);
-#pragma unroll
-        for (int o = 1; o < P; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        u = bet[tk] * (u - d * dot);
-      }
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        S[i] = fmaf(kr[i], u, d * S[i]);             o0 = fmaf(S[i], qr[i], o0);
-        S[i + 1] = fmaf(kr[i + 1], u, d * S[i + 1]); o1 = fmaf(S[i + 1], qr[i + 1], o1);
-        S[i + 2] = fmaf(kr[i + 2], u, d * S[i + 2]); o2 = fmaf(S[i + 2], qr[i + 2], o2);
-        S[i + 3] = fmaf(kr[i + 3], u, d * S[i + 3]); o3 = fmaf(S[i + 3], qr[i + 3], o3);
-      }
-      float o_ = (o0 + o1) + (o2 + o3);
-#pragma unroll
-      for (int o = 1; o < P; o <<= 1) o_ += __shfl_xor_sync(0xffffffffu, o_, o);
-      if (r == 0 && valid) p.out[(long)(start + c0 + tk) * p.ldo + (long)h * p.vdim + col] = o_;
+      for (int i = 0; i < 32; ++i) S[i] = fmaf(k_[i], u, d * S[i]);
     }
   }
   if (valid) {
