@@ -266,11 +266,13 @@ __global__ void sink_attention_merge_kernel(const float* __restrict__ part, int 
 // matrix state per head, carried from token to token:  S <- decay S + k u^T,  o = S^T q,  u = v or
 // u = beta (v - (decay S)^T k).  The columns of S evolve independently, so a block owns a slice of the value
 // columns of one head of one sequence and walks the sequence's tokens in order.  A column is held by P threads, each
-// with 32 rows of it in registers (dim <= 32 P); their partial dot products meet in a butterfly over the P lanes.
-// The slot keeps S between steps as [H][32][vdim][P] (row r * 32 + i of column c at ((h * 32 + i) * vdim + c) * P + r),
+// with LS_R rows of it in registers (dim <= LS_R P, P a power of two up to a warp); their partial dot products meet
+// in a butterfly over the P lanes.  The walk is a chain of dependent steps, so what counts is its length per token:
+// few rows per thread, and many warps per scheduler to fill the waits.
+// The slot keeps S between steps as [H][LS_R][vdim][P] (row r LS_R + i of column c at ((h LS_R + i) vdim + c) P + r),
 // which makes the loads and stores of a warp contiguous; a sequence that starts at position 0 starts from zero.
 // q and k may be shared by `rep` heads, passed through silu, and scaled to unit length per head at load.
-constexpr int LS_CT = 16, LS_THREADS = 128;   // LS_CT * 32 P must be a multiple of LS_THREADS
+constexpr int LS_CT = 16, LS_THREADS = 256, LS_R = 8, LS_RS = 12;   // LS_RS: pitch of a thread's rows in shared memory
 struct StateP {
   const float* q; long ldq;
   const float* k; long ldk;
@@ -290,32 +292,33 @@ struct StateP {
 };
 template <int P>
 __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
-  // Tokens are staged LS_CT at a time.  The raw q, k, v, decay and beta inputs of the NEXT group are requested from
+  // Tokens are staged CT at a time.  The raw q, k, v, decay and beta inputs of the NEXT group are requested from
   // global memory into registers before the current group is walked, so their latency hides behind the walk.
   // Per token, with S the state before it:  dk = S^T k, dq = S^T q (one pass, one butterfly for both),
   // u = beta (v - decay dk) (or v),  o = decay dq + u (k . q),  S <- decay S + k u^T  — o does not wait for the update.
-  constexpr int CB = LS_THREADS / P, RS = 36, LD = P * RS, DKP = P * 32;
-  constexpr int NQK = LS_CT * DKP / LS_THREADS, NV = (LS_CT * CB + LS_THREADS - 1) / LS_THREADS;
-  __shared__ __align__(16) float ks[LS_CT][LD], qs[LS_CT][LD];
-  __shared__ float vs[LS_CT][CB];
-  __shared__ float dec[LS_CT], bet[LS_CT], kq[LS_CT];
+  constexpr int CB = LS_THREADS / P, LD = P * LS_RS, DKP = P * LS_R;
+  constexpr int CT = P >= 32 ? LS_CT / 2 : LS_CT;       // tokens per group: the staged rows fit static shared memory
+  constexpr int NQK = (CT * DKP + LS_THREADS - 1) / LS_THREADS, NV = (CT * CB + LS_THREADS - 1) / LS_THREADS;
+  __shared__ __align__(16) float ks[CT][LD], qs[CT][LD];
+  __shared__ float vs[CT][CB];
+  __shared__ float dec[CT], bet[CT], kq[CT];
   const int start = p.seqs[2 * blockIdx.x], rows = p.seqs[2 * blockIdx.x + 1];
   const int h = blockIdx.y, hk = h / p.rep;
   const int cj = threadIdx.x / P, r = threadIdx.x % P, col = blockIdx.z * CB + cj;
   const bool valid = col < p.vdim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float S[32];
+  float S[LS_R];
   float* st = p.state + (long)p.slot[start] * p.slot_stride;
   if (p.pos[start] > 0 && valid) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) S[i] = st[(((long)h * 32 + i) * p.vdim + col) * P + r];
+    for (int i = 0; i < LS_R; ++i) S[i] = st[(((long)h * LS_R + i) * p.vdim + col) * P + r];
   } else {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) S[i] = 0.f;
+    for (int i = 0; i < LS_R; ++i) S[i] = 0.f;
   }
   float rk[NQK], rq[NQK], rv[NV], ra = 0.f, rb = 0.f;
-  auto request = [&](int c0) {               // raw inputs of tokens c0 .. c0 + LS_CT - 1 (zeros past the end)
-    const int nc = min(LS_CT, rows - c0);
+  auto request = [&](int c0) {               // raw inputs of tokens c0 .. c0 + CT - 1 (zeros past the end)
+    const int nc = min(CT, rows - c0);
 #pragma unroll
     for (int n = 0; n < NQK; ++n) {
       const int e = threadIdx.x + n * LS_THREADS, tk = e / DKP, i = e % DKP;
@@ -338,19 +341,21 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
   const float A = p.decay_const ? 0.f : expf(bf2f(p.A_log[h])), dtb = p.decay_const ? 0.f : bf2f(p.dt_bias[h]);
   const float dconst = p.decay_const ? p.decay_const[h] : 0.f;
   request(0);
-  for (int c0 = 0; c0 < rows; c0 += LS_CT) {
-    const int nc = min(LS_CT, rows - c0);
+  for (int c0 = 0; c0 < rows; c0 += CT) {
+    const int nc = min(CT, rows - c0);
     __syncthreads();                          // the walk over the previous group is over
 #pragma unroll
     for (int n = 0; n < NQK; ++n) {
       const int e = threadIdx.x + n * LS_THREADS, tk = e / DKP, i = e % DKP;
-      ks[tk][(i >> 5) * RS + (i & 31)] = p.act ? silu_exact(rk[n]) : rk[n];
-      qs[tk][(i >> 5) * RS + (i & 31)] = p.act ? silu_exact(rq[n]) : rq[n];
+      if (e < CT * DKP) {
+        ks[tk][(i / LS_R) * LS_RS + (i % LS_R)] = p.act ? silu_exact(rk[n]) : rk[n];
+        qs[tk][(i / LS_R) * LS_RS + (i % LS_R)] = p.act ? silu_exact(rq[n]) : rq[n];
+      }
     }
 #pragma unroll
     for (int n = 0; n < NV; ++n) {
       const int e = threadIdx.x + n * LS_THREADS;
-      if (e < LS_CT * CB) vs[e / CB][e % CB] = p.act ? silu_exact(rv[n]) : rv[n];
+      if (e < CT * CB) vs[e / CB][e % CB] = p.act ? silu_exact(rv[n]) : rv[n];
     }
     if ((int)threadIdx.x < nc) {
       dec[threadIdx.x] = p.decay_const ? dconst : expf(-A * softplus_exact(ra + dtb));
@@ -362,7 +367,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       if (p.unit_eps > 0.f) {
         float sk = 0.f, sq = 0.f;
         for (int i = lane; i < p.dim; i += 32) {
-          const float a = ks[tk][(i >> 5) * RS + (i & 31)], b = qs[tk][(i >> 5) * RS + (i & 31)];
+          const float a = ks[tk][(i / LS_R) * LS_RS + (i % LS_R)], b = qs[tk][(i / LS_R) * LS_RS + (i % LS_R)];
           sk = fmaf(a, a, sk); sq = fmaf(b, b, sq);
         }
         ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps);
@@ -370,7 +375,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       }
       float dot = 0.f;
       for (int i = lane; i < p.dim; i += 32) {
-        const int at = (i >> 5) * RS + (i & 31);
+        const int at = (i / LS_R) * LS_RS + (i % LS_R);
         const float a = ks[tk][at] * ik, b = qs[tk][at] * iq;
         ks[tk][at] = a; qs[tk][at] = b;
         dot = fmaf(a, b, dot);
@@ -379,22 +384,20 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       if (lane == 0) kq[tk] = dot;
     }
     __syncthreads();
-    if (c0 + LS_CT < rows) request(c0 + LS_CT);
+    if (c0 + CT < rows) request(c0 + CT);
     for (int tk = 0; tk < nc; ++tk) {
-      const float* kr = &ks[tk][r * RS];
-      const float* qr = &qs[tk][r * RS];
+      const float4 k0 = *reinterpret_cast<const float4*>(&ks[tk][r * LS_RS]), k1 = *reinterpret_cast<const float4*>(&ks[tk][r * LS_RS + 4]);
+      const float4 q0 = *reinterpret_cast<const float4*>(&qs[tk][r * LS_RS]), q1 = *reinterpret_cast<const float4*>(&qs[tk][r * LS_RS + 4]);
+      const float k_[LS_R] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+      const float q_[LS_R] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
       const float d = dec[tk];
-      float k_[32];
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;       // two running sums per dot: short dependency chains
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {          // four running sums per dot over i mod 4: short dependency chains
-        const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
-        const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
-        k_[i] = k4.x; k_[i + 1] = k4.y; k_[i + 2] = k4.z; k_[i + 3] = k4.w;
-        a0 = fmaf(S[i], k4.x, a0); a1 = fmaf(S[i + 1], k4.y, a1); a2 = fmaf(S[i + 2], k4.z, a2); a3 = fmaf(S[i + 3], k4.w, a3);
-        b0 = fmaf(S[i], q4.x, b0); b1 = fmaf(S[i + 1], q4.y, b1); b2 = fmaf(S[i + 2], q4.z, b2); b3 = fmaf(S[i + 3], q4.w, b3);
+      for (int i = 0; i < LS_R; i += 2) {
+        a0 = fmaf(S[i], k_[i], a0); a1 = fmaf(S[i + 1], k_[i + 1], a1);
+        b0 = fmaf(S[i], q_[i], b0); b1 = fmaf(S[i + 1], q_[i + 1], b1);
       }
-      float dk = (a0 + a1) + (a2 + a3), dq = (b0 + b1) + (b2 + b3);
+      float dk = a0 + a1, dq = b0 + b1;
 #pragma unroll
       for (int o = 1; o < P; o <<= 1) {
         dk += __shfl_xor_sync(0xffffffffu, dk, o);
@@ -404,12 +407,12 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       if (p.delta) u = bet[tk] * (u - d * dk);
       if (r == 0 && valid) p.out[(long)(start + c0 + tk) * p.ldo + (long)h * p.vdim + col] = fmaf(u, kq[tk], d * dq);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) S[i] = fmaf(k_[i], u, d * S[i]);
+      for (int i = 0; i < LS_R; ++i) S[i] = fmaf(k_[i], u, d * S[i]);
     }
   }
   if (valid) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) st[(((long)h * 32 + i) * p.vdim + col) * P + r] = S[i];
+    for (int i = 0; i < LS_R; ++i) st[(((long)h * LS_R + i) * p.vdim + col) * P + r] = S[i];
   }
 }
 
@@ -592,15 +595,20 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
                          const float* b, long ldb, int delta, void* st) {
   B200_REQUIRE(q && k && v && out && state && seqs && slot && pos && n_seq > 0 && H > 0 && rep > 0 && H % rep == 0,
                "lm_linear_state: bad argument");
-  B200_REQUIRE(dim > 0 && dim <= 256 && vdim > 0, "lm_linear_state: key size %d not supported (at most 256)", dim);
+  B200_REQUIRE(dim > 0 && dim <= 32 * LS_R && vdim > 0, "lm_linear_state: key size %d not supported (at most %d)", dim, 32 * LS_R);
   B200_REQUIRE(decay_const || (a && A_log && dt_bias), "lm_linear_state: a decay per head, or the inputs of a computed one");
   StateP p{q, ldq, k, ldk, v, ldv, out, ldo, state, slot_stride, seqs, slot, pos, H, rep, dim, vdim, act, unit_eps, q_scale,
            decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta};
   const cudaStream_t cs = (cudaStream_t)st;
-  if (dim <= 32) linear_state_kernel<1><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS)), LS_THREADS, 0, cs>>>(p);
-  else if (dim <= 64) linear_state_kernel<2><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 2)), LS_THREADS, 0, cs>>>(p);
-  else if (dim <= 128) linear_state_kernel<4><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 4)), LS_THREADS, 0, cs>>>(p);
-  else linear_state_kernel<8><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / 8)), LS_THREADS, 0, cs>>>(p);
+  const dim3 block(LS_THREADS);
+#define LS_LAUNCH(PP) linear_state_kernel<PP><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / PP)), block, 0, cs>>>(p)
+  if (dim <= LS_R) LS_LAUNCH(1);
+  else if (dim <= 2 * LS_R) LS_LAUNCH(2);
+  else if (dim <= 4 * LS_R) LS_LAUNCH(4);
+  else if (dim <= 8 * LS_R) LS_LAUNCH(8);
+  else if (dim <= 16 * LS_R) LS_LAUNCH(16);
+  else LS_LAUNCH(32);
+#undef LS_LAUNCH
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -419,11 +419,22 @@ class SinkAttention:
                     ops.head_post(og.view(mm, rep * dv), o[a:a + mm, g * rep * dv:(g + 1) * rep * dv], dv=dv)
 
 
+STATE_ROWS = 8     # rows of a matrix state's column that one thread holds (csrc/mixer_ops.cu: LS_R)
+
+
 def state_lanes(dim: int) -> int:
-    """threads that share a column of a matrix state (32 rows each): the layout of the state in the slot"""
-    if dim > 256:
-        raise ValueError(f"a matrix state with {dim} rows is not supported (at most 256)")
-    return 1 if dim <= 32 else 2 if dim <= 64 else 4 if dim <= 128 else 8
+    """threads that share a column of a matrix state (STATE_ROWS rows each; a power of two up to a warp): it fixes
+    the layout of the state in the slot, [heads][STATE_ROWS][vdim][lanes]"""
+    if dim > 32 * STATE_ROWS:
+        raise ValueError(f"a matrix state with {dim} rows is not supported (at most {32 * STATE_ROWS})")
+    lanes = 1
+    while lanes * STATE_ROWS < dim:
+        lanes *= 2
+    return lanes
+
+
+def state_floats(heads: int, dim: int, vdim: int) -> int:
+    return heads * STATE_ROWS * vdim * state_lanes(dim)
 
 
 class GatedDeltaRule:
@@ -443,7 +454,7 @@ class GatedDeltaRule:
         self.n_in, self.n_out = self.n_conv + 2 * self.H + self.n_v, self.n_v
         self.kv_dim = 0
         self.conv_floats = max(self.taps - 1, 0) * self.n_conv
-        self.state_floats = self.conv_floats + self.H * 32 * self.vdim * state_lanes(self.dim)
+        self.state_floats = self.conv_floats + state_floats(self.H, self.dim, self.vdim)
         self.w: Dict[str, torch.Tensor] = {}
 
     def in_rows(self, name: str) -> int:
@@ -483,7 +494,7 @@ class DecayedState:
         self.in_names, self.out_name = ["q", "k", "v", "g"], "o"
         self.n_in, self.n_out = 2 * self.n_qk + 2 * self.n_v, self.n_v
         self.kv_dim = 0
-        self.state_floats = self.H * 32 * self.vdim * state_lanes(self.dim)
+        self.state_floats = state_floats(self.H, self.dim, self.vdim)
         self.w: Dict[str, torch.Tensor] = {}
         self._decay_dev = None
 

@@ -278,7 +278,7 @@ def test_matrix_state_in_portions_and_slots(d, dv, H, rep, kind):
     """the state of a sequence survives from step to step in its slot; a slot that held another sequence starts anew"""
     eng = _eng()
     ops = eng.ops
-    from mlx_vlm_b200.models.decoder_blocks import state_lanes
+    from mlx_vlm_b200.models.decoder_blocks import state_floats
     T, Hk = 45, H // rep
     g = torch.Generator().manual_seed(d + dv)
     q, k = torch.randn(T, Hk, d, generator=g), torch.randn(T, Hk, d, generator=g)
@@ -286,7 +286,7 @@ def test_matrix_state_in_portions_and_slots(d, dv, H, rep, kind):
     a, b = torch.randn(T, H, generator=g), torch.randn(T, H, generator=g)
     A_log, dt = (torch.randn(H, generator=g) * 0.5).bfloat16(), torch.randn(H, generator=g).bfloat16()
     decay_h = torch.rand(H, generator=g) * 0.5 + 0.5
-    floats = H * 32 * dv * state_lanes(d)
+    floats = state_floats(H, d, dv)
     pool = _Pool(slots=3, state=floats + 3)
     st = pool.state[:, 3:3 + floats]
     if kind == "delta":

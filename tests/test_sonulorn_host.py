@@ -77,13 +77,13 @@ def test_model_layout_matches_the_checkpoint_names():
     assert [(r.layer, r.repetition, r.kv_base) for r in m.runs] == [(0, 0, 0), (1, 0, 1), (0, 1, 1), (1, 1, 2), (0, 2, 2),
                                                                     (1, 2, 3), (2, None, 3)]
     assert m.n_cache_layers == 4 and m.row_dim == 28
-    s0 = 1 * 60 + 2 * 56 + 4 * 32 * 6 * 1
-    s1 = 2 * 32 * 10 * 1
+    s0 = 1 * 60 + 2 * 56 + 4 * 8 * 6 * 1
+    s1 = 2 * 8 * 10 * 1
     assert (L0.state_floats, L1.state_floats, L2.state_floats) == (s0, s1, 0)
     assert [r.state_base for r in m.runs] == [0, s0, s0 + s1, 2 * s0 + s1, 2 * (s0 + s1), 3 * s0 + 2 * s1, 3 * (s0 + s1)]
     assert m.state_floats == 3 * (s0 + s1)
     from mlx_vlm_b200.models.decoder_blocks import SharedInputLayer, state_lanes
-    assert [state_lanes(d) for d in (1, 32, 33, 64, 65, 128, 129, 256)] == [1, 1, 2, 2, 4, 4, 8, 8]
+    assert [state_lanes(d) for d in (1, 8, 9, 16, 17, 64, 65, 128, 129, 256)] == [1, 1, 2, 2, 4, 8, 16, 16, 32, 32]
     with pytest.raises(ValueError):
         state_lanes(257)
     with pytest.raises(ValueError):
