@@ -430,40 +430,51 @@ struct HeadPostP {
   float* out; long ldo;
 };
 __global__ void head_post_kernel(HeadPostP p) {
+  // a norm group of up to 1024 numbers belongs to one warp (blockIdx.y counts warps' worth of groups), a longer one
+  // to a whole block (blockIdx.y = the group): a step of one token still spreads over many blocks
+  __shared__ float red[32];
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int span = p.span > 0 ? p.span : p.dv, groups = p.n / span;
-  const float* o = p.o + (long)t * p.ldi;
+  const bool wide = span > 1024;
+  const int gi = wide ? (int)blockIdx.y : (int)blockIdx.y * nw + warp;
+  if (gi >= groups) return;                    // whole warps (or, wide, whole blocks) leave together
+  const int me = wide ? threadIdx.x : lane, step = wide ? blockDim.x : 32;
+  const float* o = p.o + (long)t * p.ldi + (long)gi * span;
   const float* g = p.gate ? p.gate + (long)t * p.ldg : nullptr;
-  float* out = p.out + (long)t * p.ldo;
-  for (int gi = warp; gi < groups; gi += nw) {
-    float inv = 1.f;
-    if (p.span > 0) {
-      float ss = 0.f;
-      for (int i = lane; i < span; i += 32) { const float v = o[gi * span + i]; ss = fmaf(v, v, ss); }
-      inv = 1.0f / sqrtf(warp_sum(ss) / (float)span + p.eps);
+  float* out = p.out + (long)t * p.ldo + (long)gi * span;
+  float inv = 1.f;
+  if (p.span > 0) {
+    float ss = 0.f;
+    for (int i = me; i < span; i += step) { const float v = o[i]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    if (wide) {                                // fixed order: lanes, then the warps one after the other
+      if (lane == 0) red[warp] = ss;
+      __syncthreads();
+      ss = 0.f;
+      for (int w = 0; w < nw; ++w) ss += red[w];
     }
-    for (int i = lane; i < span; i += 32) {
-      const int c = gi * span + i;
-      float v = o[c] * inv;
-      if (p.w) v *= bf2f(p.w[c % p.w_len]);
-      if (g) {
-        const float z = g[p.gate_per_head ? c / p.dv : c];
-        v *= p.gate_silu ? silu_exact(z) : sigmoid_exact(z);
-      }
-      out[c] = v * p.scale;
+    inv = 1.0f / sqrtf(ss / (float)span + p.eps);
+  }
+  for (int i = me; i < span; i += step) {
+    const int c = gi * span + i;
+    float v = o[i] * inv;
+    if (p.w) v *= bf2f(p.w[c % p.w_len]);
+    if (g) {
+      const float z = g[p.gate_per_head ? c / p.dv : c];
+      v *= p.gate_silu ? silu_exact(z) : sigmoid_exact(z);
     }
+    out[i] = v * p.scale;
   }
 }
 
 // gated feed-forward activation with clamps: g = min(a, lim), u = clamp(b, -lim, lim), y = g sigmoid(alpha g) (u + 1)
 __global__ void glu_clamp_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
                                  float alpha, float* __restrict__ Y, long ldy, int n) {
-  const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float g = fminf(G[(long)t * ldg + i], lim);
-    const float u = fminf(fmaxf(U[(long)t * ldu + i], -lim), lim);
-    Y[(long)t * ldy + i] = g * sigmoid_exact(alpha * g) * (u + 1.0f);
-  }
+  const int t = blockIdx.x, i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float g = fminf(G[(long)t * ldg + i], lim);
+  const float u = fminf(fmaxf(U[(long)t * ldu + i], -lim), lim);
+  Y[(long)t * ldy + i] = g * sigmoid_exact(alpha * g) * (u + 1.0f);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -635,7 +646,8 @@ int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, con
   B200_REQUIRE(span == 0 || n % span == 0, "lm_head_post: norm groups of %d numbers in rows of %d", span, n);
   B200_REQUIRE(!w || w_len > 0, "lm_head_post: a weight needs its length");
   HeadPostP p{o, ldi, gate, ldg, (const bf16*)w, w_len, eps, span, gate_per_head, gate_silu, dv, n, scale, out, ldo};
-  head_post_kernel<<<T, 256, 0, (cudaStream_t)st>>>(p);
+  const int grp = span > 0 ? span : dv, groups = n / grp;
+  head_post_kernel<<<dim3(T, grp > 1024 ? groups : cdiv(groups, 8)), 256, 0, (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
@@ -643,7 +655,7 @@ int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, con
 int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float* Y, long ldy,
                       int n, int T, void* st) {
   B200_REQUIRE(G && U && Y && T > 0 && n > 0, "lm_glu_clamp: bad argument");
-  glu_clamp_kernel<<<T, 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, Y, ldy, n);
+  glu_clamp_kernel<<<dim3(T, cdiv(n, 256)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, Y, ldy, n);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -336,8 +336,13 @@ def test_head_post_and_clamped_activation():
     ops.head_post(dev(o), out[:, 4:], dv=dv, gate=dev(gate), w=dev(wall, torch.bfloat16), eps=1e-3, span=H * dv)
     want = O.norm(o.double(), wall.double(), 1e-3) * torch.sigmoid(gate.double())
     assert (host(eng, out)[:, 4:] - want).abs().max() < 1e-5
-    a, b = torch.randn(T, 33, generator=g) * 2, torch.randn(T, 33, generator=g) * 2
-    y = dev(torch.zeros(T, 33))
+    # a norm group longer than a warp's share is summed by a whole block
+    big, gbig, wbig = torch.randn(T, 3000, generator=g), torch.randn(T, 3000, generator=g), torch.randn(3000, generator=g).bfloat16()
+    out = dev(torch.zeros(T, 3000))
+    ops.head_post(dev(big), out, dv=1500, gate=dev(gbig), w=dev(wbig, torch.bfloat16), eps=1e-5, span=3000, scale=0.5)
+    assert (host(eng, out) - O.norm(big.double(), wbig.double(), 1e-5) * torch.sigmoid(gbig.double()) * 0.5).abs().max() < 1e-5
+    a, b = torch.randn(T, 700, generator=g) * 2, torch.randn(T, 700, generator=g) * 2
+    y = dev(torch.zeros(T, 700))
     ops.glu_clamp(dev(a), dev(b), 1.25, 1.702, y)
     gg, uu = a.double().clamp(max=1.25), b.double().clamp(-1.25, 1.25)
     assert (host(eng, y) - gg * torch.sigmoid(1.702 * gg) * (uu + 1)).abs().max() < 1e-5
