@@ -538,8 +538,8 @@ extern "C" {
 int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
                        const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
                        int act, int T, void* st) {
-  B200_REQUIRE(U && w && Y && state && slot && pos && first && seqs && T > 0 && n_seq > 0 && C > 0 && taps > 0,
-               "lm_short_conv: bad argument");
+  B200_REQUIRE(U && w && Y && (state || taps == 1) && slot && pos && first && seqs && T > 0 && n_seq > 0 && C > 0 && taps > 0,
+               "lm_short_conv: bad argument");     // one tap keeps nothing between steps
   ConvP p{U, ldu, (const bf16*)w, Y, ldy, state, slot_stride, slot, pos, first, C, taps, act};
   const int by = cdiv(C, 256) < 8 ? cdiv(C, 256) : 8;
   short_conv_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(p);

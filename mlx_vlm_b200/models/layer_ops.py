@@ -281,7 +281,8 @@ class LayerOps:
         first, seqs, G = ctx.seq_tables()
         Y = self.empty((T, C))
         self._ok(self.lib.b200_lm_short_conv(U.data_ptr(), U.stride(0), w.data_ptr(), Y.data_ptr(), Y.stride(0),
-                                             state.data_ptr(), state.stride(0), ctx.slot.data_ptr(), ctx.pos.data_ptr(),
+                                             state.data_ptr() if state.numel() else 0, state.stride(0), ctx.slot.data_ptr(),
+                                             ctx.pos.data_ptr(),
                                              first.data_ptr(), seqs.data_ptr(), G, C, w.shape[1], int(act), T, self.s),
                  "lm_short_conv")
         return Y

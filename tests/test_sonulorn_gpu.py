@@ -524,6 +524,10 @@ OTHER = {
     "one head everywhere": config([L_attn(heads=1, kv_heads=1, block=9), L_light(heads=1),
                                    L_par(left=attn(heads=1, kv_heads=1, conv=2), right=delta(heads=1, kv_heads=1, conv=2))],
                                   loop=(0, 2, 2)),
+    "one tap, no feed-forward anywhere": config([L_par(ff=False, left=attn(heads=2, kv_heads=1, dim=12, vdim=20, rot=6, conv=1),
+                                                       right=delta(heads=3, kv_heads=3, dim=20, vdim=12, conv=1)),
+                                                 L_attn(ff=False, heads=5, kv_heads=5, dim=10, vdim=14, rot=10, block=2), L_light(ff=False)],
+                                                loop=(0, 2, 2), width=50, vocab=37),
     "equal sizes": config([L_attn(heads=2, kv_heads=2, dim=32, vdim=32, rot=32, block=32), L_light(heads=2, dim=32, vdim=32),
                            L_par(left=attn(heads=2, kv_heads=2, dim=32, vdim=32, rot=32, conv=4),
                                  right=delta(heads=2, kv_heads=2, dim=32, vdim=32, conv=4), ls=1.0, rs=1.0)],
@@ -544,6 +548,8 @@ def test_other_sizes(name):
     assert rel(run_alone(model, toks), ref) < TOL["float32"]
     assert rel(run_alone(model, toks, [40] + [1] * 35), ref) < TOL["float32"]
     assert rel(run_alone(model, toks, [7, 2, 66]), ref) < TOL["float32"]
+    served, _ = build(cfg, "bfloat16", seed=7)
+    assert rel(run_alone(served, toks, [40] + [1] * 35), ref) < TOL["bfloat16"]
 
 
 # ------------------------------------------------------------------------------------------------ generation
