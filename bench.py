@@ -541,7 +541,7 @@ def _sonulorn_config(z):
     H, G, d = z["heads"], z["kv_heads"], z["dim"]
     att = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "rot": {"base": 1000000.0, "dims": d // 2}, "scale": d ** -0.5}
     mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
-    left = dict(att, conv=3)
+    left = dict(att, conv=4)
     right = {"heads": H, "kv_heads": max(1, H // 2), "dim": d, "vdim": d, "conv": 4}
     layers = [{"type": "parallel", "mixer": {"left": left, "left_scale": 0.7, "right": right, "right_scale": 0.7}, "mlp": mlp},
               {"type": "lightning", "mixer": {"heads": H, "dim": d, "vdim": d,

@@ -385,9 +385,12 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     }
     __syncthreads();
     if (c0 + CT < rows) request(c0 + CT);
-    for (int tk = 0; tk < nc; ++tk) {
-      const float4 k0 = *reinterpret_cast<const float4*>(&ks[tk][r * LS_RS]), k1 = *reinterpret_cast<const float4*>(&ks[tk][r * LS_RS + 4]);
-      const float4 q0 = *reinterpret_cast<const float4*>(&qs[tk][r * LS_RS]), q1 = *reinterpret_cast<const float4*>(&qs[tk][r * LS_RS + 4]);
+    float* op = p.out + (long)(start + c0) * p.ldo + (long)h * p.vdim + col;
+    const float* kp = &ks[0][r * LS_RS];
+    const float* qp = &qs[0][r * LS_RS];
+    for (int tk = 0; tk < nc; ++tk, op += p.ldo, kp += LD, qp += LD) {
+      const float4 k0 = *reinterpret_cast<const float4*>(kp), k1 = *reinterpret_cast<const float4*>(kp + 4);
+      const float4 q0 = *reinterpret_cast<const float4*>(qp), q1 = *reinterpret_cast<const float4*>(qp + 4);
       const float k_[LS_R] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
       const float q_[LS_R] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
       const float d = dec[tk];
@@ -405,7 +408,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       }
       float u = vs[tk][cj];
       if (p.delta) u = bet[tk] * (u - d * dk);
-      if (r == 0 && valid) p.out[(long)(start + c0 + tk) * p.ldo + (long)h * p.vdim + col] = fmaf(u, kq[tk], d * dq);
+      if (r == 0 && valid) *op = fmaf(u, kq[tk], d * dq);
 #pragma unroll
       for (int i = 0; i < LS_R; ++i) S[i] = fmaf(k_[i], u, d * S[i]);
     }

@@ -1,4 +1,4 @@
-"""Sonulorn `Model`: the per-model contract of the package (`language_model`, `get_input_embeddings`, `sanitize`,
+"""Sonulorn `Model`: the per-model surface of the package (`language_model`, `get_input_embeddings`, `sanitize`,
 `load_weights`, `engine`, `config`) for a text-only decoder whose layers read ONE normed input with all their
 sublayers (decoder_blocks.SharedInputLayer): softmax attention with a sink logit and block-local keys, a decayed
 outer-product state, an attention beside a gated delta rule, a clamped gated feed-forward.  A span of layers may run
@@ -161,7 +161,7 @@ class Model:
         eng.stream.synchronize()
         return self
 
-    # ------------------------------------------------------------------ contract
+    # ------------------------------------------------------------------ inputs
     def get_input_embeddings(self, input_ids=None, pixel_values=None, **kwargs) -> InputEmbeddingsFeatures:
         """text only: the scaled embedding rows (1, T, width) fp32"""
         if pixel_values is not None:

@@ -27,7 +27,7 @@ def attn(heads=4, kv_heads=2, dim=16, vdim=24, rot=8, base=5000.0, block=None, c
     return m
 
 
-def delta(heads=4, kv_heads=2, dim=24, vdim=16, conv=4):
+def delta(heads=4, kv_heads=2, dim=24, vdim=16, conv=3):
     return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv}
 
 
@@ -41,7 +41,7 @@ def L_attn(ff=True, **kw):
 
 def L_par(ff=True, left=None, right=None, ls=0.7, rs=0.6):
     return {"type": "parallel", "mlp": mlp() if ff else None,
-            "mixer": {"left": left or attn(heads=3, kv_heads=3, dim=16, vdim=8, rot=16, conv=3), "left_scale": ls,
+            "mixer": {"left": left or attn(heads=3, kv_heads=3, dim=16, vdim=8, rot=16, conv=2), "left_scale": ls,
                       "right": right or delta(), "right_scale": rs}}
 
 

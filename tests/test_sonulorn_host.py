@@ -23,7 +23,7 @@ def delta(**kw):
     return m
 
 
-MLP = {"kind": "dense", "ff": 12, "limit": 1.5}
+MLP = {"kind": "dense", "ff": 12, "limit": 2.0}
 
 
 def layers():
@@ -177,4 +177,4 @@ def test_restatement_pieces():
     W = {"gate": torch.randn(12, 20, generator=g, dtype=torch.float64), "up": torch.randn(12, 20, generator=g, dtype=torch.float64),
          "down": torch.eye(12, dtype=torch.float64)}
     y = O.clamped_glu(n, W, "", MLP)
-    assert y.max() <= 1.5 * 1.0 * 2.5 + 1e-9                 # g <= limit, sigmoid <= 1, u + 1 <= limit + 1
+    assert y.max() <= 2.0 * 1.0 * 3.0 + 1e-9                 # g <= limit, sigmoid <= 1, u + 1 <= limit + 1
