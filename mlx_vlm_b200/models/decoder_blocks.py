@@ -310,10 +310,11 @@ class SinkAttention:
 
     def __init__(self, index: int, cfg: dict, width: int, gate: str = "element"):
         self.index, self.W, self.gate = index, width, gate
-        self.H, self.G, self.dim, self.vdim = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
+        self.H, self.dim = int(cfg["heads"]), int(cfg["dim"])
+        self.G, self.vdim = int(cfg.get("kv_heads", self.H)), int(cfg.get("vdim", self.dim))
         if self.H % self.G:
             raise ValueError(f"layer {index}: {self.H} query heads do not divide over {self.G} key/value heads")
-        self.scale = float(cfg["scale"])
+        self.scale = float(cfg.get("scale", float(self.dim) ** -0.5))
         rot = cfg.get("rot") or {}
         self.rot_base, self.rot_dims = float(rot.get("base", 10000.0)), int(rot.get("dims", 0))
         self.chunk = int((cfg.get("mask") or {}).get("size", 0))
@@ -445,7 +446,8 @@ class GatedDeltaRule:
 
     def __init__(self, index: int, cfg: dict, width: int, unit_eps: float = 1e-6):
         self.index, self.W, self.unit_eps = index, width, unit_eps
-        self.H, self.G, self.dim, self.vdim, self.taps = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"], int(cfg["conv"])
+        self.H, self.dim, self.taps = int(cfg["heads"]), int(cfg["dim"]), int(cfg.get("conv") or 1)
+        self.G, self.vdim = int(cfg.get("kv_heads", self.H)), int(cfg.get("vdim", self.dim))
         if self.H % self.G:
             raise ValueError(f"layer {index}: {self.H} value heads do not divide over {self.G} query/key heads")
         self.n_qk, self.n_v = self.G * self.dim, self.H * self.vdim
@@ -486,8 +488,10 @@ class DecayedState:
 
     def __init__(self, index: int, cfg: dict, width: int):
         self.index, self.W = index, width
-        self.H, self.dim, self.vdim = cfg["heads"], cfg["dim"], cfg["vdim"]
-        self.decay = [float(d) for d in cfg["decay"]]
+        self.H, self.dim = int(cfg["heads"]), int(cfg["dim"])
+        self.vdim = int(cfg.get("vdim", self.dim))
+        decay = cfg["decay"]
+        self.decay = [float(d) for d in decay] if isinstance(decay, (list, tuple)) else [float(decay)] * self.H
         if len(self.decay) != self.H:
             raise ValueError(f"layer {index}: {len(self.decay)} decays for {self.H} heads")
         self.n_qk, self.n_v = self.H * self.dim, self.H * self.vdim
