@@ -974,7 +974,9 @@ int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw
     dim3 grid(cdiv(N, GV_WARPS * GV_R), 1, batch);
     const cudaStream_t cs = (cudaStream_t)st;
     dim3 gridk(cdiv(N, GK_RB), 1, batch);
-    const bool one_chunk = K <= GK_KC;     // measured: the block-wide kernel wins while a weight row is one chunk
+    // measured: the block-wide kernel wins while a weight row is one chunk; it also takes the products with long
+    // rows but so few of them that a warp per two rows would leave most of the GPU without a block
+    const bool one_chunk = K <= GK_KC || (long)grid.x * batch < 148;
     if (M <= 1 && one_chunk) gemm_skinny_blk_kernel<1><<<gridk, 256, 0, cs>>>(p);
     else if (M <= 2 && one_chunk) gemm_skinny_blk_kernel<2><<<gridk, 256, 0, cs>>>(p);
     else if (M <= 4 && one_chunk) gemm_skinny_blk_kernel<4><<<gridk, 256, 0, cs>>>(p);

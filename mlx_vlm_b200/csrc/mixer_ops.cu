@@ -130,7 +130,8 @@ struct SinkAttnP {
   float scale;
   int chunk, window;
   float* part; int n_split;        // n_split > 1: [T][H][n_split][vdim + 2] = (acc.., max, sum)
-};
+  int vec;                         // key and value columns of every row start on 16-byte boundaries and are whole
+};                                 // 16-byte vectors: rows are staged with 16-byte loads
 template <typename CT>
 __global__ void sink_attention_kernel(SinkAttnP<CT> p) {
   extern __shared__ float sm[];
@@ -164,13 +165,37 @@ __global__ void sink_attention_kernel(SinkAttnP<CT> p) {
   for (int k0 = lo + blockIdx.z * SA_KT; k0 <= ps; k0 += SA_KT * p.n_split) {
     const int nk = min(SA_KT, ps + 1 - k0);
     __syncthreads();
-    for (int e = threadIdx.x; e < nk * dim; e += blockDim.x) {
-      const int j = e / dim, i = e - j * dim;
-      keys[j * ldk + i] = ld_row(base + (long)(k0 + j) * p.tok_stride + koff + i);
-    }
-    for (int e = threadIdx.x; e < nk * vdim; e += blockDim.x) {
-      const int j = e / vdim, i = e - j * vdim;
-      vals[j * vdim + i] = ld_row(base + (long)(k0 + j) * p.tok_stride + voff + i);
+    if (p.vec) {                              // several independent 16-byte loads in flight per thread
+      constexpr int PER = 16 / (int)sizeof(CT);
+      const int kv = dim / PER, vv = vdim / PER, per_row = kv + vv;
+#pragma unroll 4
+      for (int e = threadIdx.x; e < nk * per_row; e += blockDim.x) {
+        const int j = e / per_row, c = e - j * per_row;
+        const bool is_key = c < kv;
+        const int i = (is_key ? c : c - kv) * PER;
+        const uint4 raw = *reinterpret_cast<const uint4*>(base + (long)(k0 + j) * p.tok_stride + (is_key ? koff : voff) + i);
+        float* dst = is_key ? keys + j * ldk + i : vals + j * vdim + i;
+        if (sizeof(CT) == 2) {
+          float f[8];
+          unpack8(raw, f);
+          *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
+        } else {
+          *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y),
+                                                        __uint_as_float(raw.z), __uint_as_float(raw.w));
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int e = threadIdx.x; e < nk * dim; e += blockDim.x) {
+        const int j = e / dim, i = e - j * dim;
+        keys[j * ldk + i] = ld_row(base + (long)(k0 + j) * p.tok_stride + koff + i);
+      }
+#pragma unroll 4
+      for (int e = threadIdx.x; e < nk * vdim; e += blockDim.x) {
+        const int j = e / vdim, i = e - j * vdim;
+        vals[j * vdim + i] = ld_row(base + (long)(k0 + j) * p.tok_stride + voff + i);
+      }
     }
     __syncthreads();
     if (!live) continue;
@@ -448,6 +473,7 @@ __global__ void head_post_kernel(HeadPostP p) {
   float inv = 1.f;
   if (p.span > 0) {
     float ss = 0.f;
+#pragma unroll 4
     for (int i = me; i < span; i += step) { const float v = o[i]; ss = fmaf(v, v, ss); }
     ss = warp_sum(ss);
     if (wide) {                                // fixed order: lanes, then the warps one after the other
@@ -458,6 +484,7 @@ __global__ void head_post_kernel(HeadPostP p) {
     }
     inv = 1.0f / sqrtf(ss / (float)span + p.eps);
   }
+#pragma unroll 4
   for (int i = me; i < span; i += step) {
     const int c = gi * span + i;
     float v = o[i] * inv;
@@ -585,12 +612,14 @@ int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cach
   if (cache_bf16) {
     if (first_use_on_device(&g_sink_attr_bf16))
       B200_CUDA(cudaFuncSetAttribute(sink_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    SinkAttnP<bf16> p{q, ldq, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split};
+    const int vec = dim % 8 == 0 && vdim % 8 == 0 && tok_stride % 8 == 0 && slot_stride % 8 == 0 && ((uintptr_t)cache & 15) == 0;
+    SinkAttnP<bf16> p{q, ldq, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split, vec};
     sink_attention_kernel<bf16><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   } else {
     if (first_use_on_device(&g_sink_attr_f32))
       B200_CUDA(cudaFuncSetAttribute(sink_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    SinkAttnP<float> p{q, ldq, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split};
+    const int vec = dim % 4 == 0 && vdim % 4 == 0 && tok_stride % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)cache & 15) == 0;
+    SinkAttnP<float> p{q, ldq, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split, vec};
     sink_attention_kernel<float><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   }
   B200_CHECK_LAUNCH();

@@ -368,6 +368,19 @@ def test_product_added_to_its_output_rows(M):
         assert (host(eng, z) - (yy[:, 8:].double() @ wide[:, :K].double().T + bias.double())).abs().max() < tol * 10
 
 
+@pytest.mark.parametrize("M", [1, 2, 4, 7])
+def test_product_with_long_rows_and_few_of_them(M):
+    """a decode-step product whose weight has few rows of many columns (several staging chunks per row)"""
+    eng = _eng()
+    g = torch.Generator().manual_seed(M)
+    K, N_ = 4104, 24
+    W = (torch.randn(N_, K, generator=g) / 64).bfloat16()
+    y, x0 = torch.randn(M, K, generator=g), torch.randn(M, N_, generator=g)
+    x = dev(x0)
+    eng.ops.linear(dev(y), dev(W, torch.bfloat16), out=x, add=True)
+    assert (host(eng, x) - (x0.double() + y.double() @ W.double().T)).abs().max() < 1e-4
+
+
 # ------------------------------------------------------------------------------------------------ the model
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_whole_prompt_and_every_layer_run(dtype):
