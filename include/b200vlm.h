@@ -458,12 +458,14 @@ int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cach
                            void* stream);
 /* per head a (dim, vdim) state carried through each sequence: S <- decay S + k u^T, out = S^T q, u = v or
  * (delta) beta (v - (decay S)^T k); decay per head (decay_const) or exp(-exp(A_log) softplus(a + dt_bias)) per
- * token; beta = sigmoid(b) or 1; q, k shared by `rep` heads, optionally silu'd (act) and scaled to unit length */
+ * token; beta = sigmoid(b) or 1; q, k shared by `rep` heads, optionally silu'd (act) and scaled to unit length.
+ * prep != NULL (a prompt step; T tokens): scratch of T * (2 (H / rep) dim + H / rep + 2 H) floats — the per-token work
+ * (activation, unit lengths, k . q, decay, beta) runs first as one parallel pass and the walk reads its results */
 int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv, float* out, long ldo,
                          float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
                          int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
                          const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
-                         const float* b, long ldb, int delta, void* stream);
+                         const float* b, long ldb, int delta, float* prep, int T, void* stream);
 /* operands of the tensor-core attention of a prompt step: out[(t, r)] = bf16 of q[t][r * dim .. + dim) padded to Kp;
  * P[(t, r)][j] = softmax over the visible keys key0 + j (and sink[r]) of scale * S[(t, r)][j], bf16, zero elsewhere */
 int b200_lm_heads_to_bf16(const float* q, long ldq, int rep, int dim, void* out, int Kp, int T, void* stream);

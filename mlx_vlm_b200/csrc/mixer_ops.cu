@@ -309,12 +309,66 @@ struct StateP {
   int H, rep, dim, vdim;
   int act;                          // silu on q, k, v at load
   float unit_eps, q_scale;          // unit_eps > 0: q, k <- x / sqrt(sum x^2 + unit_eps); q also times q_scale
+  // prepared inputs (a prompt step: one parallel pass over all tokens does the per-token work first): q, k are already
+  // activated and scaled, and these hold k . q [T][H / rep], the decay [T][H] and beta [T][H]; NULL: made here
+  const float *kq_in, *dec_in, *bet_in;
   const float* decay_const;         // [H], or NULL: decay = exp(-exp(A_log[h]) softplus(a[t][h] + dt_bias[h]))
   const float* a; long lda;
   const bf16 *A_log, *dt_bias;
   const float* b; long ldb;         // beta = sigmoid(b[t][h]); NULL: 1
   int delta;
 };
+// The per-token work of a prompt step in one parallel pass: q, k activated and scaled to unit length (a warp per
+// token and q/k head, the same order of sums as the walk's own staging), k . q, the decay and beta of every head.
+struct StatePrepP {
+  const float* q; long ldq;
+  const float* k; long ldk;
+  float *qn, *kn; long ldn;         // [T][Hk * dim]
+  float *kq, *dec, *bet;            // [T][Hk], [T][H], [T][H]
+  int H, Hk, dim, act;
+  float unit_eps, q_scale;
+  const float* decay_const;
+  const float* a; long lda;
+  const bf16 *A_log, *dt_bias;
+  const float* b; long ldb;
+};
+__global__ void state_prep_kernel(StatePrepP p) {
+  const long t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int hk = warp; hk < p.Hk; hk += nw) {
+    const float* kr = p.k + t * p.ldk + (long)hk * p.dim;
+    const float* qr = p.q + t * p.ldq + (long)hk * p.dim;
+    float* ko = p.kn + t * p.ldn + (long)hk * p.dim;
+    float* qo = p.qn + t * p.ldn + (long)hk * p.dim;
+    float ik = 1.f, iq = 1.f;
+    if (p.unit_eps > 0.f) {
+      float sk = 0.f, sq = 0.f;
+      for (int i = lane; i < p.dim; i += 32) {
+        float a = kr[i], b = qr[i];
+        if (p.act) { a = silu_exact(a); b = silu_exact(b); }
+        sk = fmaf(a, a, sk); sq = fmaf(b, b, sq);
+      }
+      ik = 1.0f / sqrtf(warp_sum(sk) + p.unit_eps);
+      iq = p.q_scale / sqrtf(warp_sum(sq) + p.unit_eps);
+    }
+    float dot = 0.f;
+    for (int i = lane; i < p.dim; i += 32) {
+      float a = kr[i], b = qr[i];
+      if (p.act) { a = silu_exact(a); b = silu_exact(b); }
+      a *= ik; b *= iq;
+      ko[i] = a; qo[i] = b;
+      dot = fmaf(a, b, dot);
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) p.kq[t * p.Hk + hk] = dot;
+  }
+  for (int h = threadIdx.x; h < p.H; h += blockDim.x) {
+    p.dec[t * p.H + h] = p.decay_const ? p.decay_const[h]
+        : expf(-expf(bf2f(p.A_log[h])) * softplus_exact(p.a[t * p.lda + h] + bf2f(p.dt_bias[h])));
+    p.bet[t * p.H + h] = p.b ? sigmoid_exact(p.b[t * p.ldb + h]) : 1.f;
+  }
+}
+
 template <int P>
 __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
   // Tokens are staged CT at a time.  The raw q, k, v, decay and beta inputs of the NEXT group are requested from
@@ -341,7 +395,8 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
 #pragma unroll
     for (int i = 0; i < LS_R; ++i) S[i] = 0.f;
   }
-  float rk[NQK], rq[NQK], rv[NV], ra = 0.f, rb = 0.f;
+  float rk[NQK], rq[NQK], rv[NV], ra = 0.f, rb = 0.f, rkq = 0.f;
+  const bool raw = p.kq_in == nullptr, act_qk = raw && p.act;
   auto request = [&](int c0) {               // raw inputs of tokens c0 .. c0 + CT - 1 (zeros past the end)
     const int nc = min(CT, rows - c0);
 #pragma unroll
@@ -359,11 +414,15 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     }
     if ((int)threadIdx.x < nc) {
       const long t = start + c0 + threadIdx.x;
-      if (!p.decay_const) ra = p.a[t * p.lda + h];
-      if (p.b) rb = p.b[t * p.ldb + h];
+      if (p.kq_in) {
+        ra = p.dec_in[t * p.H + h]; rb = p.bet_in[t * p.H + h]; rkq = p.kq_in[t * (p.H / p.rep) + hk];
+      } else {
+        if (!p.decay_const) ra = p.a[t * p.lda + h];
+        if (p.b) rb = p.b[t * p.ldb + h];
+      }
     }
   };
-  const float A = p.decay_const ? 0.f : expf(bf2f(p.A_log[h])), dtb = p.decay_const ? 0.f : bf2f(p.dt_bias[h]);
+  const float A = (p.decay_const || !raw) ? 0.f : expf(bf2f(p.A_log[h])), dtb = (p.decay_const || !raw) ? 0.f : bf2f(p.dt_bias[h]);
   const float dconst = p.decay_const ? p.decay_const[h] : 0.f;
   request(0);
   for (int c0 = 0; c0 < rows; c0 += CT) {
@@ -373,8 +432,8 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     for (int n = 0; n < NQK; ++n) {
       const int e = threadIdx.x + n * LS_THREADS, tk = e / DKP, i = e % DKP;
       if (e < CT * DKP) {
-        ks[tk][(i / LS_R) * LS_RS + (i % LS_R)] = p.act ? silu_exact(rk[n]) : rk[n];
-        qs[tk][(i / LS_R) * LS_RS + (i % LS_R)] = p.act ? silu_exact(rq[n]) : rq[n];
+        ks[tk][(i / LS_R) * LS_RS + (i % LS_R)] = act_qk ? silu_exact(rk[n]) : rk[n];
+        qs[tk][(i / LS_R) * LS_RS + (i % LS_R)] = act_qk ? silu_exact(rq[n]) : rq[n];
       }
     }
 #pragma unroll
@@ -383,11 +442,15 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       if (e < CT * CB) vs[e / CB][e % CB] = p.act ? silu_exact(rv[n]) : rv[n];
     }
     if ((int)threadIdx.x < nc) {
-      dec[threadIdx.x] = p.decay_const ? dconst : expf(-A * softplus_exact(ra + dtb));
-      bet[threadIdx.x] = p.b ? sigmoid_exact(rb) : 1.f;
+      if (raw) {
+        dec[threadIdx.x] = p.decay_const ? dconst : expf(-A * softplus_exact(ra + dtb));
+        bet[threadIdx.x] = p.b ? sigmoid_exact(rb) : 1.f;
+      } else {
+        dec[threadIdx.x] = ra; bet[threadIdx.x] = rb; kq[threadIdx.x] = rkq;
+      }
     }
     __syncthreads();
-    for (int tk = warp; tk < nc; tk += LS_THREADS / 32) {      // a warp per token row: lengths and k . q in a fixed order
+    for (int tk = warp; raw && tk < nc; tk += LS_THREADS / 32) {      // a warp per token row: lengths and k . q in a fixed order
       float ik = 1.f, iq = 1.f;
       if (p.unit_eps > 0.f) {
         float sk = 0.f, sq = 0.f;
@@ -408,7 +471,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       dot = warp_sum(dot);
       if (lane == 0) kq[tk] = dot;
     }
-    __syncthreads();
+    if (raw) __syncthreads();
     if (c0 + CT < rows) request(c0 + CT);
     float* op = p.out + (long)(start + c0) * p.ldo + (long)h * p.vdim + col;
     const float* kp = &ks[0][r * LS_RS];
@@ -635,14 +698,25 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
                          float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
                          int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
                          const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
-                         const float* b, long ldb, int delta, void* st) {
+                         const float* b, long ldb, int delta, float* prep, int T, void* st) {
   B200_REQUIRE(q && k && v && out && state && seqs && slot && pos && n_seq > 0 && H > 0 && rep > 0 && H % rep == 0,
                "lm_linear_state: bad argument");
   B200_REQUIRE(dim > 0 && dim <= 32 * LS_R && vdim > 0, "lm_linear_state: key size %d not supported (at most %d)", dim, 32 * LS_R);
   B200_REQUIRE(decay_const || (a && A_log && dt_bias), "lm_linear_state: a decay per head, or the inputs of a computed one");
   StateP p{q, ldq, k, ldk, v, ldv, out, ldo, state, slot_stride, seqs, slot, pos, H, rep, dim, vdim, act, unit_eps, q_scale,
-           decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta};
+           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta};
   const cudaStream_t cs = (cudaStream_t)st;
+  if (prep) {     // scratch of T * (2 Hk dim + Hk + 2 H) floats: the per-token work runs first, over all tokens at once
+    B200_REQUIRE(T > 0, "lm_linear_state: the prepared path needs the number of tokens");
+    const int Hk = H / rep;
+    const long n = (long)Hk * dim;
+    float *qn = prep, *kn = qn + (long)T * n, *kq = kn + (long)T * n, *dec = kq + (long)T * Hk, *bet = dec + (long)T * H;
+    StatePrepP pp{q, ldq, k, ldk, qn, kn, n, kq, dec, bet, H, Hk, dim, act, unit_eps, q_scale, decay_const, a, lda,
+                  (const bf16*)A_log, (const bf16*)dt_bias, b, ldb};
+    state_prep_kernel<<<T, 128, 0, cs>>>(pp);
+    B200_CHECK_LAUNCH();
+    p.q = qn; p.ldq = n; p.k = kn; p.ldk = n; p.kq_in = kq; p.dec_in = dec; p.bet_in = bet;
+  }
   const dim3 block(LS_THREADS);
 #define LS_LAUNCH(PP) linear_state_kernel<PP><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / PP)), block, 0, cs>>>(p)
   if (dim <= LS_R) LS_LAUNCH(1);

@@ -325,11 +325,14 @@ class LayerOps:
     def linear_state(self, q, k, v, out, state, ctx, *, H, rep, dim, vdim, act=False, unit_eps=0.0, q_scale=1.0,
                      decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False):
         _, seqs, G = ctx.seq_tables()
+        T, Hk = q.shape[0], H // rep
+        # a prompt step does the per-token work (activation, unit lengths, k . q, decay, beta) in one parallel pass first
+        prep = self.empty((T * (2 * Hk * dim + Hk + 2 * H),)) if T > SKINNY_ROWS else None
         self._ok(self.lib.b200_lm_linear_state(
             q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
             state.data_ptr(), state.stride(0), seqs.data_ptr(), G, ctx.slot.data_ptr(), ctx.pos.data_ptr(), H, rep, dim,
             vdim, int(act), float(unit_eps), float(q_scale), N.ptr(decay_const), N.ptr(a), a.stride(0) if a is not None else 0,
-            N.ptr(A_log), N.ptr(dt_bias), N.ptr(b), b.stride(0) if b is not None else 0, int(delta), self.s),
+            N.ptr(A_log), N.ptr(dt_bias), N.ptr(b), b.stride(0) if b is not None else 0, int(delta), N.ptr(prep), T, self.s),
             "lm_linear_state")
 
     def head_post(self, o, out, *, dv, gate=None, gate_per_head=False, gate_silu=False, w=None, eps=0.0, span=0,
