@@ -346,6 +346,12 @@ def test_head_post_and_clamped_activation():
     ops.glu_clamp(dev(a), dev(b), 1.25, 1.702, y)
     gg, uu = a.double().clamp(max=1.25), b.double().clamp(-1.25, 1.25)
     assert (host(eng, y) - gg * torch.sigmoid(1.702 * gg) * (uu + 1)).abs().max() < 1e-5
+    # many rows of whole 16-byte vectors (a prompt step) take four columns per thread; column ranges of wider rows
+    wide = torch.randn(40, 3 * 64, generator=g) * 2
+    wd, y = dev(wide), dev(torch.zeros(40, 64 + 4))
+    ops.glu_clamp(wd[:, :64], wd[:, 128:], 1.25, 1.702, y[:, 4:])
+    gg, uu = wide[:, :64].double().clamp(max=1.25), wide[:, 128:].double().clamp(-1.25, 1.25)
+    assert (host(eng, y)[:, 4:] - gg * torch.sigmoid(1.702 * gg) * (uu + 1)).abs().max() < 1e-5
 
 
 @pytest.mark.parametrize("M", [1, 3, 12, 40, 150])
